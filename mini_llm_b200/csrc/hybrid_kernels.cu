@@ -12,6 +12,11 @@
 //                     token, gated experts fed the token times its score, a shared expert with an
 //                     output gate
 //   scaled_add        x += a * u + b * v on the 32-bit residual stream
+//   head_norm_store   queries and keys divided by their root mean square per head (no gain), and the
+//                     keys and values into their cache pages
+// capped_attention also takes a chunked mask (a query sees the keys of its own block of `chunk`
+// positions only) and a gate per (token, head) whose sigmoid multiplies the head's result;
+// linear_recurrence also takes a decay per key channel instead of one per head.
 // Every kernel is templated on the element type of the activations (float: the true 32-bit path;
 // bfloat16: the serving path) and is launched as a programmatic dependent of the kernel before it.
 #include "common.cuh"
@@ -99,6 +104,65 @@ extern "C" int mllm_hybrid_rotary_store(void* qkv, long ld, int k_off, int v_off
 }
 
 // ---------------------------------------------------------------------------
+// Queries and keys over their root mean square, per head and without a gain:
+// x / sqrt(mean(x^2) + eps) over the head's `dim` entries, in place; the normed keys and the values
+// then go to the token's place in the pages.  A row of `qkv` is laid out as for rotary_store.  One
+// block per token, a warp per head in turn; sums in 32-bit.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_store_kernel(T* __restrict__ qkv, long ld, int k_off, int v_off, int heads, int kv_heads, int dim, int vdim,
+                       float eps, const int* __restrict__ positions, const int* __restrict__ token_item,
+                       const int* __restrict__ block_table, int max_blocks, int page_size, T* __restrict__ k_pages,
+                       T* __restrict__ v_pages, int writes) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p = positions[t];
+    T* row = qkv + (long)t * ld;
+    long slot = 0;
+    if (writes) slot = (long)block_table[(long)token_item[t] * max_blocks + p / page_size] * page_size + (p % page_size);
+    for (int head = warp; head < heads + kv_heads; head += 4) {
+        const bool is_key = head >= heads;
+        T* x = is_key ? row + k_off + (long)(head - heads) * dim : row + (long)head * dim;
+        float sq = 0.0f;
+        for (int d = lane; d < dim; d += 32) {
+            const float v = to_f32(x[d]);
+            sq = fmaf(v, v, sq);
+        }
+        const float inv = eps >= 0.0f ? 1.0f / sqrtf(warp_sum(sq) / (float)dim + eps) : 1.0f;      // (eps < 0: stored as they are)
+        T* dst = k_pages + (slot * kv_heads + (head - heads)) * dim;
+        for (int d = lane; d < dim; d += 32) {
+            const T v = from_f32<T>(to_f32(x[d]) * inv);
+            x[d] = v;
+            if (is_key && writes) dst[d] = v;
+        }
+    }
+    if (writes)
+        for (int c = threadIdx.x; c < kv_heads * vdim; c += blockDim.x) v_pages[slot * kv_heads * vdim + c] = row[v_off + c];
+}
+
+extern "C" int mllm_hybrid_head_norm_store(void* qkv, long ld, int k_off, int v_off, int heads, int kv_heads, int dim, int vdim,
+                                           float eps, const int* positions, const int* token_item, const int* block_table,
+                                           int max_blocks, int page_size, void* k_pages, void* v_pages, int writes, int n_tokens,
+                                           int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0) return fail("head_norm_store: sizes must be positive");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DT_F32)
+        launch_kernel(g_dependent_launch != 0, head_norm_store_kernel<float>, dim3(n_tokens), dim3(128), 0, s, (float*)qkv, ld, k_off,
+                      v_off, heads, kv_heads, dim, vdim, eps, positions, token_item, block_table, max_blocks, page_size,
+                      (float*)k_pages, (float*)v_pages, writes);
+    else if (dtype == DT_BF16)
+        launch_kernel(g_dependent_launch != 0, head_norm_store_kernel<bf16>, dim3(n_tokens), dim3(128), 0, s, (bf16*)qkv, ld, k_off,
+                      v_off, heads, kv_heads, dim, vdim, eps, positions, token_item, block_table, max_blocks, page_size,
+                      (bf16*)k_pages, (bf16*)v_pages, writes);
+    else
+        return fail("head_norm_store: unknown dtype");
+    return check_launch("head_norm_store_kernel");
+}
+
+// ---------------------------------------------------------------------------
 // Causal attention with capped scores, one block per (token, head): the plain form, which takes
 // every size.  score = cap * tanh((q . k) * scale / cap) (cap <= 0: no cap); the query at position
 // p sees keys max(0, p - window + 1) .. p (window <= 0: all).  Four warps take the keys in turn,
@@ -108,13 +172,22 @@ constexpr int CAP_MAX_HEAD = 256;
 
 __device__ __forceinline__ float capped(float s, float cap, float inv_cap) { return cap > 0.0f ? cap * tanhf(s * inv_cap) : s; }
 
+// The first key the query at position p sees: the last `window` positions (window <= 0: all), and
+// within its own block of `chunk` positions counted from 0 (chunk <= 0: no blocks).
+__device__ __forceinline__ int first_visible(int p, int window, int chunk) {
+    int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    if (chunk > 0) lo = max(lo, (p / chunk) * chunk);
+    return lo;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 capped_attention_plain_kernel(T* __restrict__ out, long ld_out, const T* __restrict__ q, long ld_q,
                               const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                               const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
                               const int* __restrict__ token_item, int n_heads, int n_kv_heads, int dim, int vdim,
-                              int page_size, float scale, float cap, int window) {
+                              int page_size, float scale, float cap, int window, int chunk,
+                              const float* __restrict__ gate, long ld_gate) {
     dependents_may_start();
     wait_for_earlier_kernels();
     constexpr int R = CAP_MAX_HEAD / 32;
@@ -132,7 +205,7 @@ capped_attention_plain_kernel(T* __restrict__ out, long ld_out, const T* __restr
         acc[i] = 0.0f;
     }
     float m = -INFINITY, l = 0.0f;
-    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int lo = first_visible(p, window, chunk);
     for (int j = lo + warp; j <= p; j += 4) {
         const long slot = (long)bt[j / page_size] * page_size + (j % page_size);
         const T* kr = k_pages + (slot * n_kv_heads + hk) * dim;
@@ -170,11 +243,12 @@ capped_attention_plain_kernel(T* __restrict__ out, long ld_out, const T* __restr
         wgt[w] = sm_m[w] == -INFINITY ? 0.0f : expf(sm_m[w] - big);
         total += sm_l[w] * wgt[w];
     }
+    const float open = gate != nullptr ? sigmoid_f(gate[(long)t * ld_gate + h]) : 1.0f;
     for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
         float o = 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; w++) o += sm_acc[w][d] * wgt[w];
-        out[(long)t * ld_out + (long)h * vdim + d] = from_f32<T>(o / total);
+        out[(long)t * ld_out + (long)h * vdim + d] = from_f32<T>(o / total * open);
     }
 }
 
@@ -211,8 +285,8 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
                               const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                               const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
                               const int* __restrict__ token_item, int n_tokens, int n_heads, int n_kv_heads, int dim,
-                              int vdim, int page_size, float scale, float cap, int window, int tokens_per_block,
-                              int heads_per_block) {
+                              int vdim, int page_size, float scale, float cap, int window, int chunk,
+                              const float* __restrict__ gate, long ld_gate, int tokens_per_block, int heads_per_block) {
     dependents_may_start();
     wait_for_earlier_kernels();
     constexpr int ROWS = TILE_WARPS * R;
@@ -269,16 +343,16 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
         key_vec[i] = value_vec[i] = make_uint4(0, 0, 0, 0);
     }
     const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
-    auto fetch = [&](const int* bt, int base, int p_last) {
+    auto fetch = [&](const int* bt, int base, int p_last, int p_lo) {
 #pragma unroll
         for (int i = 0; i < MAXV; i++) {
             const int kp = base + key_row[i], vp = base + value_row[i];
-            if (key_row[i] >= 0 && kp <= p_last) {
+            if (key_row[i] >= 0 && kp <= p_last && kp >= p_lo) {
                 const int block = page_shift >= 0 ? kp >> page_shift : kp / page_size;
                 const long slot = (long)bt[block] * page_size + (kp - block * page_size);
                 key_vec[i] = *reinterpret_cast<const uint4*>(k_pages + (slot * n_kv_heads + hk) * dim + key_col[i]);
             }
-            if (value_row[i] >= 0 && vp <= p_last) {
+            if (value_row[i] >= 0 && vp <= p_last && vp >= p_lo) {
                 const int block = page_shift >= 0 ? vp >> page_shift : vp / page_size;
                 const long slot = (long)bt[block] * page_size + (vp - block * page_size);
                 value_vec[i] = *reinterpret_cast<const uint4*>(v_pages + (slot * n_kv_heads + hk) * vdim + value_col[i]);
@@ -294,10 +368,10 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
         int run_last = run_first;
         while (run_last + 1 < n_tok && token_item[first_token + run_last + 1] == item) run_last++;
         const int p_first = positions[first_token + run_first], p_last = positions[first_token + run_last];
-        const int lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+        const int lo = first_visible(p_first, window, chunk);
         const int* bt = block_table + (long)item * max_blocks;
         const int first_base = (lo / TILE_KEYS) * TILE_KEYS;
-        fetch(bt, first_base, p_last);
+        fetch(bt, first_base, p_last, lo);          // (pages before the first visible key may be gone)
         for (int base = first_base; base <= p_last; base += TILE_KEYS) {
             __syncthreads();                                  // the block before has been read; q_rows are written
             const int n_keys = min(TILE_KEYS, p_last + 1 - base);
@@ -308,13 +382,13 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
             }
             __syncthreads();
             // the next block's rows are asked for now and arrive while this one is worked on
-            if (base + TILE_KEYS <= p_last) fetch(bt, base + TILE_KEYS, p_last);
+            if (base + TILE_KEYS <= p_last) fetch(bt, base + TILE_KEYS, p_last, lo);
             // which of the warp's rows see a key of this block at all
             bool any = false, seen[R];
             int first_seen[R];
 #pragma unroll
             for (int s = 0; s < R; s++) {
-                first_seen[s] = (window > 0 && row_pos[s] - window + 1 > 0) ? row_pos[s] - window + 1 : 0;
+                first_seen[s] = first_visible(row_pos[s], window, chunk);
                 seen[s] = row_item[s] == item && base <= row_pos[s] && base + TILE_KEYS > first_seen[s];
                 any = any || seen[s];
             }
@@ -383,7 +457,7 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
         const int r = warp + s * TILE_WARPS;
         if (r >= n_rows) continue;
         const int token = first_token + r / n_heads_here, head = first_head + r % n_heads_here;
-        const float inv = 1.0f / l[s];
+        const float inv = (gate != nullptr ? sigmoid_f(gate[(long)token * ld_gate + head]) : 1.0f) / l[s];
 #pragma unroll
         for (int i = 0; i < VPL; i++) {
             const int d = lane + 32 * i;
@@ -407,7 +481,7 @@ template <typename T, int R, int SIZE>
 static int launch_capped_tiles(void* out, long ld_out, const void* q, long ld_q, const void* k_pages, const void* v_pages,
                                const int* block_table, int max_blocks, const int* positions, const int* token_item, int n_tokens,
                                int n_heads, int n_kv_heads, int dim, int vdim, int page_size, float scale, float cap, int window,
-                               cudaStream_t s) {
+                               int chunk, const float* gate, long ld_gate, cudaStream_t s) {
     constexpr int ROWS = TILE_WARPS * R;
     const int group = n_heads / n_kv_heads;
     const int heads_per_block = group < ROWS ? group : ROWS;
@@ -421,7 +495,8 @@ static int launch_capped_tiles(void* out, long ld_out, const void* q, long ld_q,
     dim3 grid((n_tokens + tokens_per_block - 1) / tokens_per_block, n_kv_heads * chunks);
     launch_kernel(g_dependent_launch != 0, capped_attention_tiled_kernel<T, R, SIZE>, grid, dim3(TILE_WARPS * 32), shared, s, (T*)out,
                   ld_out, (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table, max_blocks, positions, token_item,
-                  n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, tokens_per_block, heads_per_block);
+                  n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, chunk, gate, ld_gate, tokens_per_block,
+                  heads_per_block);
     return check_launch("capped_attention_tiled_kernel");
 }
 
@@ -429,11 +504,12 @@ template <typename T>
 static int launch_capped_attention(bool tiled, void* out, long ld_out, const void* q, long ld_q, const void* k_pages,
                                    const void* v_pages, const int* block_table, int max_blocks, const int* positions,
                                    const int* token_item, int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim,
-                                   int page_size, float scale, float cap, int window, cudaStream_t s) {
+                                   int page_size, float scale, float cap, int window, int chunk, const float* gate, long ld_gate,
+                                   cudaStream_t s) {
     if (!tiled) {
         launch_kernel(g_dependent_launch != 0, capped_attention_plain_kernel<T>, dim3(n_tokens, n_heads), dim3(128), 0, s, (T*)out,
                       ld_out, (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table, max_blocks, positions,
-                      token_item, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window);
+                      token_item, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, chunk, gate, ld_gate);
         return check_launch("capped_attention_plain_kernel");
     }
     // rows a warp: four where the step has rows enough for the blocks to fill the GPU all the same
@@ -443,7 +519,7 @@ static int launch_capped_attention(bool tiled, void* out, long ld_out, const voi
     if (capped_tiled_shared(dim, vdim, per_warp) > 160 * 1024) per_warp = 2;
 #define TILES(R, SIZE)                                                                                                        \
     return launch_capped_tiles<T, R, SIZE>(out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions, token_item, \
-                                           n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, s)
+                                           n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, chunk, gate, ld_gate, s)
     const int size = (dim > vdim ? dim : vdim) <= 64 ? 64 : ((dim > vdim ? dim : vdim) <= 128 ? 128 : 256);
     if (per_warp == 4) { if (size == 64) TILES(4, 64); if (size == 128) TILES(4, 128); TILES(4, 256); }
     if (size == 64) TILES(2, 64);
@@ -455,7 +531,8 @@ static int launch_capped_attention(bool tiled, void* out, long ld_out, const voi
 extern "C" int mllm_hybrid_capped_attention(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,
                                             const void* v_pages, const int* block_table, int max_blocks, const int* positions,
                                             const int* token_item, int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim,
-                                            int page_size, float scale, float cap, int window, int tiled, int dtype, void* stream) {
+                                            int page_size, float scale, float cap, int window, int chunk, const float* gate,
+                                            long ld_gate, int tiled, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (dim <= 0 || dim > CAP_MAX_HEAD || vdim <= 0 || vdim > CAP_MAX_HEAD) return fail("capped_attention: key and value sizes must be in 1..256");
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return fail("capped_attention: heads must be a multiple of the key/value heads");
@@ -464,10 +541,12 @@ extern "C" int mllm_hybrid_capped_attention(void* out, long ld_out, const void* 
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == DT_F32)
         return launch_capped_attention<float>(tiled != 0, out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions,
-                                              token_item, n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, s);
+                                              token_item, n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, chunk, gate,
+                                              ld_gate, s);
     if (dtype == DT_BF16)
         return launch_capped_attention<bf16>(tiled != 0, out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions,
-                                             token_item, n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, s);
+                                             token_item, n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, chunk, gate,
+                                             ld_gate, s);
     return fail("capped_attention: unknown dtype");
 }
 
@@ -479,6 +558,10 @@ extern "C" int mllm_hybrid_capped_attention(void* out, long ld_out, const void* 
 //   S <- a_t S + k_t u_t^T;   out_t = S^T q_t (+ skip[h] v_t)
 // Query/key head of head h: h / (heads / qk_heads).  With unit_norm, q and k are divided by
 // sqrt(sum(x^2) + 1e-6) per head first; q is multiplied by q_scale.
+// With channel_decay the decay is one per key channel instead: gate_a [T, heads * dim] and step_bias
+// [heads * dim], a_t[i] = exp(-exp(log_rate[h]) * softplus(gate_a[t, h, i] + step_bias[h, i])), and row i of S
+// is multiplied by a_t[i] before the old column is read: S <- diag(a_t) S; u_t = b_t (v_t - S^T k_t);
+// S <- S + k_t u_t^T.
 // One block per (entry, head, slice of the value entries): a column of S belongs to LANES threads
 // of one warp, each with DPT rows in registers; both sums over the old column (with k and with q)
 // are taken in one pass, and the read-out follows from them: S_new^T q = a S^T q + u (k . q).
@@ -495,9 +578,10 @@ struct RecurrenceParams {
     int heads, qk_heads, dim, vdim;
     float q_scale;
     int delta, unit_norm, writes;
+    int channel_decay;
 };
 
-template <typename T, int DPT, int LANES, int TOK, int CPT>      // CPT: columns of the state a thread takes
+template <typename T, int DPT, int LANES, int TOK, int CPT, bool CHANNEL>      // CPT: columns of the state a thread takes
 __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams pp) {
     dependents_may_start();
     wait_for_earlier_kernels();
@@ -516,6 +600,8 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
     float* as = vs + TOK * COLS;                // [TOK] the step's gate, then the decay
     float* bs = as + TOK;                       // [TOK] the write gate, then the write strength
     float* kq = bs + TOK;                       // [TOK] k . q
+    float* gs = kq + TOK;                       // [TOK][ROW] (CHANNEL only): the decay of every key channel, laid out as ks
+    constexpr int GPER = CHANNEL ? (TOK * DPT * LANES + 127) / 128 : 1;     // decays a thread brings
     const int item = blockIdx.x, head = blockIdx.y;
     const int count = pp.item_count[item];
     if (count <= 0) return;
@@ -541,7 +627,7 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
     }
     __syncthreads();
     const float rate = expf(pp.log_rate[head]);
-    const float bias = pp.step_bias[head];
+    const float bias = CHANNEL ? 0.0f : pp.step_bias[head];
     const float skip = pp.skip != nullptr ? pp.skip[head] : 0.0f;
     const T* q = (const T*)pp.q;
     const T* k = (const T*)pp.k;
@@ -558,6 +644,7 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
     float* row_smem = ((row & 1) ? qs : ks) + row_token * ROW;
     T raw[PER], raw_v[VPER];
     float raw_a = 0.0f, raw_b = 0.0f;
+    float raw_g[GPER];
     auto ask = [&](int start) {
         const int n = min(TOK, count - start);
         const long t0 = first + start;
@@ -572,8 +659,16 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
             raw_v[i] = (tt < n && c < vdim) ? v[(t0 + tt) * pp.ld_v + (long)head * vdim + c] : from_f32<T>(0.0f);
         }
         if (threadIdx.x < n) {
-            raw_a = pp.gate_a[(t0 + threadIdx.x) * pp.ld_gate_a + head];
+            if (!CHANNEL) raw_a = pp.gate_a[(t0 + threadIdx.x) * pp.ld_gate_a + head];
             if (pp.delta) raw_b = pp.gate_b[(t0 + threadIdx.x) * pp.ld_gate_b + head];
+        }
+        if (CHANNEL) {
+#pragma unroll
+            for (int i = 0; i < GPER; i++) {
+                const int u = threadIdx.x + 128 * i, tt = u / (DPT * LANES), d = u % (DPT * LANES);
+                raw_g[i] = (tt < n && d < dim) ? pp.gate_a[(t0 + tt) * pp.ld_gate_a + (long)head * dim + d] + pp.step_bias[(long)head * dim + d]
+                                               : 0.0f;
+            }
         }
     };
     ask(0);
@@ -593,8 +688,15 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
         if (threadIdx.x < TOK) {
             // a thread a token: the step, the decay, the write strength
             const float step = softplus_f(raw_a + bias);
-            as[threadIdx.x] = expf(-rate * step);
+            as[threadIdx.x] = CHANNEL ? 1.0f : expf(-rate * step);
             bs[threadIdx.x] = pp.delta ? sigmoid_f(raw_b) : step;
+        }
+        if (CHANNEL) {
+#pragma unroll
+            for (int i = 0; i < GPER; i++) {
+                const int u = threadIdx.x + 128 * i, tt = u / (DPT * LANES), d = u % (DPT * LANES);
+                if (tt < TOK) gs[tt * ROW + (d / DPT) * PAD + d % DPT] = expf(-rate * softplus_f(raw_g[i]));
+            }
         }
         __syncthreads();
         // a warp finishes TOK / 4 tokens: unit vectors if asked, and k . q; the sums of its tokens are
@@ -649,6 +751,12 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
                 const float4 k4 = *reinterpret_cast<const float4*>(kr + r);
                 const float4 q4 = *reinterpret_cast<const float4*>(qr + r);
                 kreg[r] = k4.x, kreg[r + 1] = k4.y, kreg[r + 2] = k4.z, kreg[r + 3] = k4.w;
+                if (CHANNEL) {
+                    // every row of the state decays by its own factor first; the sums then read the decayed rows
+                    const float4 g4 = *reinterpret_cast<const float4*>(gs + tt * ROW + lane_in * PAD + r);
+#pragma unroll
+                    for (int c = 0; c < CPT; c++) s[c][r] *= g4.x, s[c][r + 1] *= g4.y, s[c][r + 2] *= g4.z, s[c][r + 3] *= g4.w;
+                }
 #pragma unroll
                 for (int c = 0; c < CPT; c++) {
                     dk[c][0] = fmaf(s[c][r], k4.x, dk[c][0]), dq[c][0] = fmaf(s[c][r], q4.x, dq[c][0]);
@@ -697,18 +805,24 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
     }
 }
 
-template <typename T, int DPT, int LANES, int TOK, int CPT>
-static int launch_recurrence(const RecurrenceParams& pp, int n_items, cudaStream_t s) {
+template <typename T, int DPT, int LANES, int TOK, int CPT, bool CHANNEL>
+static int launch_recurrence_as(const RecurrenceParams& pp, int n_items, cudaStream_t s) {
     constexpr int COLS = 128 / LANES * CPT;
     // the staged chunk, or the block's slice of the state on its way in and out, whichever is larger
-    const size_t staged = (size_t)2 * TOK * LANES * (DPT + 4) + TOK * COLS + 3 * TOK, slice = (size_t)DPT * LANES * COLS;
+    const size_t staged = (size_t)(CHANNEL ? 3 : 2) * TOK * LANES * (DPT + 4) + TOK * COLS + 3 * TOK, slice = (size_t)DPT * LANES * COLS;
     const size_t shared = sizeof(float) * (staged > slice ? staged : slice);
     dim3 grid(n_items, pp.heads, (pp.vdim + COLS - 1) / COLS);
     if (shared > 48 * 1024 &&
-        cudaFuncSetAttribute(linear_recurrence_kernel<T, DPT, LANES, TOK, CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess)
+        cudaFuncSetAttribute(linear_recurrence_kernel<T, DPT, LANES, TOK, CPT, CHANNEL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess)
         return fail("linear_recurrence: the staged rows' shared memory was refused");
-    launch_kernel(g_dependent_launch != 0, linear_recurrence_kernel<T, DPT, LANES, TOK, CPT>, grid, dim3(128), shared, s, pp);
+    launch_kernel(g_dependent_launch != 0, linear_recurrence_kernel<T, DPT, LANES, TOK, CPT, CHANNEL>, grid, dim3(128), shared, s, pp);
     return check_launch("linear_recurrence_kernel");
+}
+
+template <typename T, int DPT, int LANES, int TOK, int CPT>
+static int launch_recurrence(const RecurrenceParams& pp, int n_items, cudaStream_t s) {
+    if (pp.channel_decay) return launch_recurrence_as<T, DPT, LANES, TOK, CPT, true>(pp, n_items, s);
+    return launch_recurrence_as<T, DPT, LANES, TOK, CPT, false>(pp, n_items, s);
 }
 
 // A column of the state lies in the registers of 4 to 32 lanes of a warp.  Prompt portions: eight
@@ -749,6 +863,7 @@ extern "C" int mllm_hybrid_linear_recurrence(const RecurrenceParams* params, int
     if (pp.qk_heads <= 0 || pp.heads % pp.qk_heads != 0) return fail("linear_recurrence: heads must be a multiple of the query/key heads");
     if (pp.heads > 65535) return fail("linear_recurrence: too many heads for one launch");
     if (pp.delta && pp.gate_b == nullptr) return fail("linear_recurrence: the delta rule needs its write gates");
+    if (pp.channel_decay && pp.skip != nullptr) return fail("linear_recurrence: a decay per key channel goes with no skip");
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == DT_F32) return pick_recurrence<float>(pp, n_items, n_tokens, s);
     if (dtype == DT_BF16) return pick_recurrence<bf16>(pp, n_items, n_tokens, s);

@@ -264,8 +264,11 @@ extern "C" int mllm_sequence_causal_taps(void* out, long ld_out, const void* h, 
 //   q[t] = per head [dim | rot]: the rot part gets rotary positions and goes, in 32-bit, to
 //   q_eff[t, head, rank .. rank + rot) (the first `rank` entries of q_eff are filled by the
 //   product with the key expansion).
-// Rotary positions, interleaved: among the first rot_dims entries, (x[2i], x[2i+1]) turns by
-// position * inv_freq[i]; the rest pass unchanged.  Angles in 64-bit.
+// Rotary positions: among the first rot_dims entries, pair i turns by position * inv_freq[i] and
+// the rest pass unchanged; the pair is (x[2i], x[2i+1]) (layout 0, interleaved) or
+// (x[i], x[i + rot_dims/2]) (layout 1, halves).  Angles in 64-bit.
+// With `writes` false nothing is stored and `down` is not read (it may be null): an entry that
+// reads another entry's rows prepares its queries only.
 // One block per token.
 // ---------------------------------------------------------------------------
 template <typename T>
@@ -274,7 +277,7 @@ __global__ void latent_prepare_kernel(T* __restrict__ pages, float* __restrict__
                                       const double* __restrict__ inv_freq, const int* __restrict__ positions,
                                       const int* __restrict__ token_item, const int* __restrict__ block_table,
                                       int max_blocks, int page_size, int rank, int rot, int rot_dims, int heads, int dim,
-                                      float eps, int writes) {
+                                      float eps, int writes, int layout) {
     dependents_may_start();
     wait_for_earlier_kernels();
     __shared__ float scratch[33];
@@ -288,30 +291,45 @@ __global__ void latent_prepare_kernel(T* __restrict__ pages, float* __restrict__
         turn[i] = (float)c;
         turn[half + i] = (float)s;
     }
-    const float* mine = down + (long)t * (rank + rot);
-    float sq = 0.0f;
-    for (int d = threadIdx.x; d < rank; d += blockDim.x) sq = fmaf(mine[d], mine[d], sq);
-    const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)rank + eps);      // (its barriers also publish turn[])
+    // entry e of a rotated part: its pair's index, its partner, and whether it is the pair's second
+    auto pair_of = [&](int e, int& i, int& partner) -> bool {
+        if (layout == 0) {
+            i = e >> 1, partner = e ^ 1;
+            return (e & 1) != 0;
+        }
+        i = e < half ? e : e - half, partner = e < half ? e + half : e - half;
+        return e >= half;
+    };
     if (writes) {
+        const float* mine = down + (long)t * (rank + rot);
+        float sq = 0.0f;
+        for (int d = threadIdx.x; d < rank; d += blockDim.x) sq = fmaf(mine[d], mine[d], sq);
+        const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)rank + eps);      // (its barriers also publish turn[])
         const int page = block_table[(long)token_item[t] * max_blocks + p / page_size];
         T* row = pages + ((long)page * page_size + (p % page_size)) * (rank + rot);
         for (int d = threadIdx.x; d < rank; d += blockDim.x) row[d] = from_f32<T>(mine[d] * inv * gain[d]);
         for (int e = threadIdx.x; e < rot; e += blockDim.x) {
             float v = mine[rank + e];
             if (e < 2 * half) {
-                const float c = turn[e >> 1], s = turn[half + (e >> 1)];
-                v = (e & 1) ? v * c + mine[rank + e - 1] * s : v * c - mine[rank + e + 1] * s;
+                int i, partner;
+                const bool second = pair_of(e, i, partner);
+                const float c = turn[i], s = turn[half + i];
+                v = second ? v * c + mine[rank + partner] * s : v * c - mine[rank + partner] * s;
             }
             row[rank + e] = from_f32<T>(v);
         }
+    } else {
+        __syncthreads();                             // publishes turn[]
     }
-    for (int i = threadIdx.x; i < heads * rot; i += blockDim.x) {
-        const int head = i / rot, e = i % rot;
+    for (int u = threadIdx.x; u < heads * rot; u += blockDim.x) {
+        const int head = u / rot, e = u % rot;
         const T* from = q + (long)t * ld_q + (long)head * (dim + rot) + dim;
         float v = to_f32(from[e]);
         if (e < 2 * half) {
-            const float c = turn[e >> 1], s = turn[half + (e >> 1)];
-            v = (e & 1) ? v * c + to_f32(from[e - 1]) * s : v * c - to_f32(from[e + 1]) * s;
+            int i, partner;
+            const bool second = pair_of(e, i, partner);
+            const float c = turn[i], s = turn[half + i];
+            v = second ? v * c + to_f32(from[partner]) * s : v * c - to_f32(from[partner]) * s;
         }
         q_eff[((long)t * heads + head) * (rank + rot) + rank + e] = v;
     }
@@ -321,19 +339,21 @@ extern "C" int mllm_sequence_latent_prepare(void* pages, float* q_eff, const flo
                                             const float* gain, const double* inv_freq, const int* positions,
                                             const int* token_item, const int* block_table, int max_blocks, int page_size,
                                             int n_tokens, int rank, int rot, int rot_dims, int heads, int dim, float eps,
-                                            int writes, int dtype, void* stream) {
+                                            int writes, int layout, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
+    if (layout != 0 && layout != 1) return fail("latent_prepare: the layout of the pairs is 0 (interleaved) or 1 (halves)");
+    if (writes && down == nullptr) return fail("latent_prepare: an entry that stores its rows needs its projection");
     if (rot_dims < 0 || rot_dims > rot || rot_dims % 2 != 0) return fail("latent_prepare: rotated dimensions must be even and at most the rotated part");
     cudaStream_t s = (cudaStream_t)stream;
     const size_t shared = (size_t)(rot_dims > 0 ? rot_dims : 1) * sizeof(float);
     if (dtype == DT_F32)
         launch_kernel(g_dependent_launch != 0, latent_prepare_kernel<float>, dim3(n_tokens), dim3(128), shared, s, (float*)pages, q_eff, down, (const float*)q, ld_q, gain, inv_freq,
                                                                    positions, token_item, block_table, max_blocks, page_size,
-                                                                   rank, rot, rot_dims, heads, dim, eps, writes);
+                                                                   rank, rot, rot_dims, heads, dim, eps, writes, layout);
     else if (dtype == DT_BF16)
         launch_kernel(g_dependent_launch != 0, latent_prepare_kernel<bf16>, dim3(n_tokens), dim3(128), shared, s, (bf16*)pages, q_eff, down, (const bf16*)q, ld_q, gain, inv_freq,
                                                                   positions, token_item, block_table, max_blocks, page_size,
-                                                                  rank, rot, rot_dims, heads, dim, eps, writes);
+                                                                  rank, rot, rot_dims, heads, dim, eps, writes, layout);
     else
         return fail("latent_prepare: unknown dtype");
     return check_launch("latent_prepare_kernel");
@@ -462,7 +482,8 @@ extern "C" int mllm_sequence_head_linear(void* out, const void* a, const void* w
 // Causal attention over a shared latent, one block per (token, head).
 // Every cached token is one row [rank + rot] of the pages; the score of query (t, head)
 // against it is q_eff[t, head, :] . row * scale, and the row's first `rank` entries are its
-// value.  The query at position p sees positions 0 .. p of its own request.  Four warps take
+// value.  The query at position p sees positions 0 .. p of its own request, or the last `window`
+// of them (window <= 0: all).  Four warps take
 // the keys in turn, each with an online softmax (32-bit); their states are merged in a fixed
 // order.  out[t, head, :rank] in 32-bit.  R: 32-element pieces of a row a lane may hold.
 // ---------------------------------------------------------------------------
@@ -470,7 +491,8 @@ template <typename T, int R>
 __global__ void __launch_bounds__(128)
 latent_attention_kernel(float* __restrict__ out, const float* __restrict__ q_eff, const T* __restrict__ pages,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
-                        const int* __restrict__ token_item, int heads, int rank, int rot, int page_size, float scale) {
+                        const int* __restrict__ token_item, int heads, int rank, int rot, int page_size, float scale,
+                        int window) {
     dependents_may_start();
     wait_for_earlier_kernels();
     const int t = blockIdx.x, h = blockIdx.y;
@@ -487,7 +509,8 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ q_eff
         acc[i] = 0.0f;
     }
     float m = -INFINITY, l = 0.0f;
-    for (int j = warp; j <= p; j += 4) {
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    for (int j = lo + warp; j <= p; j += 4) {
         const T* row = pages + ((long)bt[j / page_size] * page_size + (j % page_size)) * row_width;
         float kv[R];
         float s = 0.0f;
@@ -532,18 +555,18 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ q_eff
 template <typename T>
 static int launch_latent_attention(float* out, const float* q_eff, const void* pages, const int* block_table, int max_blocks,
                                    const int* positions, const int* token_item, int n_tokens, int heads, int rank, int rot,
-                                   int page_size, float scale, cudaStream_t s) {
+                                   int page_size, float scale, int window, cudaStream_t s) {
     dim3 grid(n_tokens, heads);
     const T* pg = (const T*)pages;
     const int pieces = (rank + rot + 31) / 32;
     if (pieces <= 4)
-        launch_kernel(g_dependent_launch != 0, latent_attention_kernel<T, 4>, dim3(grid), dim3(128), 0, s, out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
+        launch_kernel(g_dependent_launch != 0, latent_attention_kernel<T, 4>, dim3(grid), dim3(128), 0, s, out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale, window);
     else if (pieces <= 8)
-        launch_kernel(g_dependent_launch != 0, latent_attention_kernel<T, 8>, dim3(grid), dim3(128), 0, s, out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
+        launch_kernel(g_dependent_launch != 0, latent_attention_kernel<T, 8>, dim3(grid), dim3(128), 0, s, out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale, window);
     else if (pieces <= 20)
-        launch_kernel(g_dependent_launch != 0, latent_attention_kernel<T, 20>, dim3(grid), dim3(128), 0, s, out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
+        launch_kernel(g_dependent_launch != 0, latent_attention_kernel<T, 20>, dim3(grid), dim3(128), 0, s, out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale, window);
     else if (pieces <= 36)
-        launch_kernel(g_dependent_launch != 0, latent_attention_kernel<T, 36>, dim3(grid), dim3(128), 0, s, out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
+        launch_kernel(g_dependent_launch != 0, latent_attention_kernel<T, 36>, dim3(grid), dim3(128), 0, s, out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale, window);
     else
         return fail("latent_attention: a cached row may hold at most 1152 entries");
     return check_launch("latent_attention_kernel");
@@ -551,17 +574,17 @@ static int launch_latent_attention(float* out, const float* q_eff, const void* p
 
 extern "C" int mllm_sequence_latent_attention(float* out, const float* q_eff, const void* pages, const int* block_table,
                                               int max_blocks, const int* positions, const int* token_item, int n_tokens,
-                                              int heads, int rank, int rot, int page_size, float scale, int dtype,
-                                              void* stream) {
+                                              int heads, int rank, int rot, int page_size, float scale, int window,
+                                              int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (heads <= 0 || heads > 65535 || rank <= 0 || rot < 0) return fail("latent_attention: bad sizes");
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == DT_F32)
         return launch_latent_attention<float>(out, q_eff, pages, block_table, max_blocks, positions, token_item, n_tokens, heads,
-                                              rank, rot, page_size, scale, s);
+                                              rank, rot, page_size, scale, window, s);
     if (dtype == DT_BF16)
         return launch_latent_attention<bf16>(out, q_eff, pages, block_table, max_blocks, positions, token_item, n_tokens, heads,
-                                             rank, rot, page_size, scale, s);
+                                             rank, rot, page_size, scale, window, s);
     return fail("latent_attention: unknown dtype");
 }
 
@@ -590,6 +613,7 @@ struct LatentTiledParams {
     float scale;
     int out_bf16;                  // `out` holds bfloat16 (the expansion that follows then runs on the tensor cores)
     int key_buffers;               // 2: the next block of cached rows is copied (cp.async) while this one is used; 1: no room for that
+    int window;                    // a query sees the last `window` positions only (<= 0: all)
 };
 
 template <typename T> struct Chunk4;
@@ -651,10 +675,11 @@ latent_attention_tiled_kernel(LatentTiledParams p) {
     const int head0 = blockIdx.y * p.HB;
     const int* bt = p.block_table + (long)item * p.max_blocks;
     int key_begin = 0, key_end = first_position + rows;            // keys [key_begin, key_end)
+    if (p.window > 0) key_begin = max(0, first_position - p.window + 1);      // (what the block's first row sees first)
     if (p.parts > 1) {
         // the token's own keys, cut into `parts` runs of whole blocks: nothing depends on a length the host knew
-        const int per_part = ((key_end + p.parts - 1) / p.parts + BK - 1) / BK * BK;
-        key_begin = blockIdx.z * per_part;
+        const int per_part = ((key_end - key_begin + p.parts - 1) / p.parts + BK - 1) / BK * BK;
+        key_begin += blockIdx.z * per_part;
         key_end = min(key_end, key_begin + per_part);
     }
     const bool empty = key_begin >= key_end;
@@ -775,7 +800,7 @@ latent_attention_tiled_kernel(LatentTiledParams p) {
 #pragma unroll
             for (int u = 0; u < BK / 32; u++) {
                 const int key = k0 + lane + 32 * u;
-                const bool seen = key < key_end && key <= row_position[r];
+                const bool seen = key < key_end && key <= row_position[r] && (p.window <= 0 || key > row_position[r] - p.window);
                 sc[u] = seen ? Ss[r * (BK + 1) + lane + 32 * u] * p.scale : -INFINITY;
                 top = fmaxf(top, sc[u]);
             }

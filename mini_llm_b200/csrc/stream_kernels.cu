@@ -1,0 +1,147 @@
+// Kernels of layers whose residual is several streams (hyper-connections), and of gated feed-forwards:
+//   streams_fill   every stream of a token starts as the token's embedded row
+//   streams_step   per token, one block: (1) if a sublayer result y is given, all streams at once from
+//                  the old ones, x_t <- sum_s mix[s, t] x_s + out[t] y; (2) if asked, the read-out
+//                  u = sum_s in[s] x_s of the (new) streams (in = null: the plain sum), stored in
+//                  32-bit and / or divided by its root mean square and multiplied by a gain, as the
+//                  input of the next sublayer.  Streams, weights and sums are 32-bit.
+//   gated_act      act(gate) * up over the two halves of a product's result
+// The normed read-out is templated on the element type of the activations (float: the true 32-bit
+// path; bfloat16: the serving path); every kernel is launched as a programmatic dependent of the
+// kernel before it.
+#include "common.cuh"
+
+MLLM_DEFINE_ERROR_API(mllm_streams)
+
+constexpr int MAX_STREAMS = 8;
+
+__global__ void streams_fill_kernel(float* __restrict__ streams, const float* __restrict__ hidden, int n_streams, int width,
+                                    long n) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;         // over tokens * width
+    if (i >= n) return;
+    const long t = i / width, c = i % width;
+    const float v = hidden[i];
+    for (int s = 0; s < n_streams; s++) streams[(t * n_streams + s) * width + c] = v;
+}
+
+extern "C" int mllm_streams_fill(float* streams, const float* hidden, int n_streams, int width, int n_tokens, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_streams <= 0 || width <= 0) return fail("streams_fill: sizes must be positive");
+    const long n = (long)n_tokens * width;
+    launch_kernel(g_dependent_launch != 0, streams_fill_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
+                  streams, hidden, n_streams, width, n);
+    return check_launch("streams_fill_kernel");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+streams_step_kernel(float* __restrict__ streams, const float* __restrict__ y, long ld_y, const float* __restrict__ mix,
+                    const float* __restrict__ w_out, int read, const float* __restrict__ w_in, float* __restrict__ u_out,
+                    long ld_u, T* __restrict__ normed, long ld_normed, const float* __restrict__ gain, float eps, int n_streams,
+                    int width) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
+    extern __shared__ float u_row[];                 // [width]: the read-out, until it is normed
+    __shared__ float scratch[33];
+    __shared__ float m[MAX_STREAMS * MAX_STREAMS], o[MAX_STREAMS], in[MAX_STREAMS];
+    const int t = blockIdx.x;
+    if (threadIdx.x < n_streams * n_streams && y != nullptr) m[threadIdx.x] = mix[threadIdx.x];
+    if (threadIdx.x < n_streams) {
+        if (y != nullptr) o[threadIdx.x] = w_out[threadIdx.x];
+        in[threadIdx.x] = w_in != nullptr ? w_in[threadIdx.x] : 1.0f;
+    }
+    __syncthreads();
+    float* mine = streams + (long)t * n_streams * width;
+    float sq = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float x[MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < MAX_STREAMS; s++) x[s] = s < n_streams ? mine[(long)s * width + c] : 0.0f;
+        if (y != nullptr) {
+            const float result = y[(long)t * ld_y + c];
+            float fresh[MAX_STREAMS];
+#pragma unroll
+            for (int to = 0; to < MAX_STREAMS; to++) {
+                if (to >= n_streams) continue;
+                float sum = 0.0f;
+#pragma unroll
+                for (int s = 0; s < MAX_STREAMS; s++)
+                    if (s < n_streams) sum = fmaf(m[s * n_streams + to], x[s], sum);
+                fresh[to] = fmaf(o[to], result, sum);
+            }
+#pragma unroll
+            for (int s = 0; s < MAX_STREAMS; s++)
+                if (s < n_streams) mine[(long)s * width + c] = x[s] = fresh[s];
+        }
+        if (read) {
+            float u = 0.0f;
+#pragma unroll
+            for (int s = 0; s < MAX_STREAMS; s++)
+                if (s < n_streams) u = fmaf(in[s], x[s], u);
+            if (u_out != nullptr) u_out[(long)t * ld_u + c] = u;
+            u_row[c] = u;
+            sq = fmaf(u, u, sq);
+        }
+    }
+    if (!read || normed == nullptr) return;
+    const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) normed[(long)t * ld_normed + c] = from_f32<T>(u_row[c] * inv * gain[c]);
+}
+
+extern "C" int mllm_streams_step(float* streams, const float* y, long ld_y, const float* mix, const float* w_out, int read,
+                                 const float* w_in, float* u_out, long ld_u, void* normed, long ld_normed, const float* gain,
+                                 float eps, int n_streams, int width, int n_tokens, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_streams <= 0 || n_streams > MAX_STREAMS) return fail("streams_step: between 1 and 8 streams");
+    if (width <= 0) return fail("streams_step: the width must be positive");
+    if (y != nullptr && (mix == nullptr || w_out == nullptr)) return fail("streams_step: a sublayer result needs its mixing weights");
+    if (normed != nullptr && (gain == nullptr || !read)) return fail("streams_step: the normed read-out needs a gain");
+    const size_t shared = (size_t)width * sizeof(float);
+    if (shared > 200 * 1024) return fail("streams_step: the row does not fit in shared memory");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DT_F32) {
+        if (shared > 48 * 1024) cudaFuncSetAttribute(streams_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        launch_kernel(g_dependent_launch != 0, streams_step_kernel<float>, dim3(n_tokens), dim3(256), shared, s, streams, y, ld_y, mix,
+                      w_out, read, w_in, u_out, ld_u, (float*)normed, ld_normed, gain, eps, n_streams, width);
+    } else if (dtype == DT_BF16) {
+        if (shared > 48 * 1024) cudaFuncSetAttribute(streams_step_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        launch_kernel(g_dependent_launch != 0, streams_step_kernel<bf16>, dim3(n_tokens), dim3(256), shared, s, streams, y, ld_y, mix,
+                      w_out, read, w_in, u_out, ld_u, (bf16*)normed, ld_normed, gain, eps, n_streams, width);
+    } else {
+        return fail("streams_step: unknown dtype");
+    }
+    return check_launch("streams_step_kernel");
+}
+
+// out[t, f] = act(gu[t, f]) * gu[t, inner + f]; act: 0 silu, 1 gelu (tanh form), 2 none
+template <typename T>
+__global__ void gated_act_kernel(T* __restrict__ out, long ld_out, const T* __restrict__ gu, long ld_gu, int inner, int act,
+                                 long n) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long t = i / inner, f = i % inner;
+    const float gate = to_f32(gu[t * ld_gu + f]), up = to_f32(gu[t * ld_gu + inner + f]);
+    const float a = act == 0 ? gate / (1.0f + expf(-gate)) : (act == 1 ? gelu_tanh_f(gate) : gate);
+    out[t * ld_out + f] = from_f32<T>(a * up);
+}
+
+extern "C" int mllm_streams_gated_act(void* out, long ld_out, const void* gu, long ld_gu, int inner, int act, int n_tokens,
+                                      int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (inner <= 0 || act < 0 || act > 2) return fail("gated_act: bad sizes or activation");
+    const long n = (long)n_tokens * inner;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DT_F32)
+        launch_kernel(g_dependent_launch != 0, gated_act_kernel<float>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, (float*)out,
+                      ld_out, (const float*)gu, ld_gu, inner, act, n);
+    else if (dtype == DT_BF16)
+        launch_kernel(g_dependent_launch != 0, gated_act_kernel<bf16>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, (bf16*)out,
+                      ld_out, (const bf16*)gu, ld_gu, inner, act, n);
+    else
+        return fail("gated_act: unknown dtype");
+    return check_launch("gated_act_kernel");
+}

@@ -43,6 +43,7 @@ LIBRARIES = {
     "fused": "fused_decode.cu",
     "sequence": "sequence_kernels.cu",
     "hybrid": "hybrid_kernels.cu",
+    "streams": "stream_kernels.cu",
 }
 
 _lock = threading.Lock()

@@ -118,14 +118,21 @@ class Kernels:
         return ops.rotary_store(qkv, k_off, v_off, heads, kv_heads, dim, vdim, rot_dims, inv_freq, amplitude, ctx.positions,
                                 ctx.token_item, cache.block_table, cache.page_size, cache.k_pages, cache.v_pages, cache.writes)
 
-    def capped_attention(self, ctx, out, q, cache, n_heads, n_kv_heads, dim, vdim, scale, cap=0.0, window=0):
+    def head_norm_store(self, ctx, cache, qkv, k_off, v_off, heads, kv_heads, dim, vdim, eps):
+        self.launches += 1
+        return ops.head_norm_store(qkv, k_off, v_off, heads, kv_heads, dim, vdim, -1.0 if eps is None else eps, ctx.positions, ctx.token_item,
+                                   cache.block_table, cache.page_size, cache.k_pages, cache.v_pages, cache.writes)
+
+    def capped_attention(self, ctx, out, q, cache, n_heads, n_kv_heads, dim, vdim, scale, cap=0.0, window=0, chunk=0,
+                         gate=None):
         """Attention whose weights stay 32-bit, with a cap on the scores and values of a size of
-        their own.  Steps with prompt portions take the tiles (tokens of a request side by side
-        share the cached rows they read); steps of single tokens, and sizes the tiles do not take,
-        one block per (token, head)."""
+        their own; the mask is causal, over the last ``window`` positions or within blocks of
+        ``chunk`` positions; ``gate`` [T, heads] opens each head's result by its sigmoid.  Steps with
+        prompt portions take the tiles (tokens of a request side by side share the cached rows they
+        read); steps of single tokens, and sizes the tiles do not take, one block per (token, head)."""
         self.launches += 1
         n = q.shape[0]
-        if (not self.plain_only and ctx.decode_only and n <= SPLIT_ATTENTION_MAX_ROWS and dim == vdim
+        if (not self.plain_only and ctx.decode_only and n <= SPLIT_ATTENTION_MAX_ROWS and dim == vdim and not chunk and gate is None
                 and dim in ops.SPLIT_ATTENTION_HEAD_SIZES and q.dtype == torch.bfloat16 and q.stride(0) % 8 == 0):
             # single tokens: each token's keys in chunks over many CTAs, merged by the last to arrive
             # (its exponentials, weights and sums are 32-bit, which this attention asks for)
@@ -140,13 +147,14 @@ class Kernels:
         tiled = not ctx.decode_only and ops.capped_attention_tiled_takes(dim, vdim, q.dtype)
         self.chose("capped_attention", "capped_attention_tiled" if tiled else "capped_attention_plain", q.shape[0], n_heads, dim, vdim)
         return ops.capped_attention(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.token_item,
-                                    n_heads, n_kv_heads, dim, vdim, cache.page_size, scale, cap, window, tiled)
+                                    n_heads, n_kv_heads, dim, vdim, cache.page_size, scale, cap, window, tiled, chunk, gate)
 
     def linear_recurrence(self, ctx, out, q, k, v, gate_a, gate_b, log_rate, step_bias, state, heads, qk_heads, dim, vdim,
-                          delta, unit_norm=False, q_scale=1.0, skip=None, writes=True):
+                          delta, unit_norm=False, q_scale=1.0, skip=None, writes=True, channel_decay=False):
         self.launches += 1
         return ops.linear_recurrence(out, q, k, v, gate_a, gate_b, log_rate, step_bias, state, ctx.item_slot, ctx.item_offset,
-                                     ctx.item_count, heads, qk_heads, dim, vdim, delta, unit_norm, q_scale, skip, writes)
+                                     ctx.item_count, heads, qk_heads, dim, vdim, delta, unit_norm, q_scale, skip, writes,
+                                     channel_decay)
 
     def route(self, x, router, shared_gate, top, choice, in_weight, out_weight):
         self.launches += 1
@@ -175,10 +183,11 @@ class Kernels:
         self.launches += 1
         return ops.scaled_add(x, u, a, v, b)
 
-    def latent_prepare(self, ctx, cache, q_eff, down, q, gain, inv_freq, rank, rot, rot_dims, heads, dim, eps):
+    def latent_prepare(self, ctx, cache, q_eff, down, q, gain, inv_freq, rank, rot, rot_dims, heads, dim, eps,
+                       layout="interleaved"):
         self.launches += 1
         return ops.latent_prepare(cache.k_pages, q_eff, down, q, gain, inv_freq, ctx.positions, ctx.token_item,
-                                  cache.block_table, cache.page_size, rank, rot, rot_dims, heads, dim, eps, cache.writes)
+                                  cache.block_table, cache.page_size, rank, rot, rot_dims, heads, dim, eps, cache.writes, layout)
 
     HEAD_LINEAR_GEMM_ROWS = 128   # from here on each head's product goes to the tensor-core kernel by itself
 
@@ -204,7 +213,7 @@ class Kernels:
         tiled = not self.plain_only and ops.latent_attention_tiled_takes(cache.k_pages, rank, rot)
         return torch.bfloat16 if tiled and self.act_dtype == torch.bfloat16 else torch.float32
 
-    def latent_attention(self, ctx, out, q_eff, cache, heads, rank, rot, scale):
+    def latent_attention(self, ctx, out, q_eff, cache, heads, rank, rot, scale, window=0):
         self.launches += 1
         n = q_eff.shape[0]
         if not self.plain_only and ops.latent_attention_tiled_takes(cache.k_pages, rank, rot):
@@ -213,7 +222,7 @@ class Kernels:
             if ctx.att_tiles is not None:
                 # prompt portions: 32 rows (tokens x heads) a block share every cached row they read
                 self.chose("latent_attention", "latent_attention_tiled", n, heads, rank + rot)
-                return ops.latent_attention_tiled(*common, tiles=ctx.att_tiles, n_tiles=ctx.n_att_tiles)
+                return ops.latent_attention_tiled(*common, tiles=ctx.att_tiles, n_tiles=ctx.n_att_tiles, window=window)
             if ctx.decode_only:
                 # single tokens: all heads of a token share the cached rows; while the (token, head
                 # block) pairs are fewer than twice the SMs, each token's keys come in parts
@@ -222,11 +231,11 @@ class Kernels:
                 scratch = self._latent_scratch(ctx.device, n * heads * parts * rank, n * heads * parts * 2) if parts > 1 else None
                 self.launches += 1 if parts > 1 else 0
                 self.chose("latent_attention", "latent_attention_tiled_parts", n, heads, rank + rot)
-                return ops.latent_attention_tiled(*common, parts=parts, scratch=scratch)
+                return ops.latent_attention_tiled(*common, parts=parts, scratch=scratch, window=window)
         self.chose("latent_attention", "latent_attention_plain", n, heads, rank + rot)
         plain_out = out if out.dtype == torch.float32 else ctx.buffer("latent_mixed_32", out.shape, torch.float32)
         ops.latent_attention_plain(plain_out, q_eff, cache.k_pages, cache.block_table, ctx.positions, ctx.token_item,
-                                   heads, rank, rot, cache.page_size, scale)
+                                   heads, rank, rot, cache.page_size, scale, window)
         if plain_out is not out:
             out.copy_(plain_out)
         return out
@@ -254,6 +263,19 @@ class Kernels:
             self._memory_passes = held = tuple(torch.empty(max(n, 1), dtype=torch.float32, device=device) for n in floats)
             self.scratch_generation += 1
         return held
+
+    # ---- residual streams, gated feed-forwards ----------------------------------------------------
+    def streams_fill(self, streams, hidden):
+        self.launches += 1
+        return ops.streams_fill(streams, hidden)
+
+    def streams_step(self, streams, **what):
+        self.launches += 1
+        return ops.streams_step(streams, **what)
+
+    def gated_act(self, out, gu, activation="silu"):
+        self.launches += 1
+        return ops.gated_act(out, gu, activation)
 
     def depth_mix(self, hidden, kept, weights, index):
         self.launches += 1

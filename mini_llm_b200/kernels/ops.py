@@ -883,18 +883,25 @@ def norm_taps_step(out, x, gain, groups, eps, w, state, token_item, item_slot, w
 
 
 _latent_prepare = Function("sequence", "mllm_sequence_latent_prepare",
-                           [P, P, P, P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P])
+                           [P, P, P, P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, P])
+ROTARY_LAYOUTS = {"interleaved": 0, "half": 1}
 
 
 def latent_prepare(pages, q_eff, down, q, gain, inv_freq, positions, token_item, block_table, page_size, rank, rot,
-                   rot_dims, heads, dim, eps, writes=True):
+                   rot_dims, heads, dim, eps, writes=True, layout="interleaved"):
     """Per token: the first ``rank`` entries of the fp32 ``down`` row, normed by their root mean square
     and times ``gain``, and its last ``rot`` entries with rotary positions, go into the token's row
     of ``pages`` [n_pages, page_size, 1, rank + rot]; the rotated part of every head's query
     (``q`` [T, heads * (dim + rot)]) gets rotary positions and goes to
-    ``q_eff`` [T, heads * (rank + rot)] (fp32), entries rank .. rank + rot of each head."""
+    ``q_eff`` [T, heads * (rank + rot)] (fp32), entries rank .. rank + rot of each head.  ``layout``: the
+    pairs that turn together are neighbours ("interleaved") or half the rotated entries apart ("half").
+    With ``writes`` false only the queries are prepared and ``down`` may be None."""
     _check(pages, "latent_prepare.pages", q.dtype)
     _check(q_eff, "latent_prepare.q_eff", torch.float32, 2)
+    if down is None:
+        if writes:
+            raise KernelError("latent_prepare: an entry that stores its rows needs its projection")
+        down = q_eff.new_empty((0, rank + rot))
     _check(down, "latent_prepare.down", torch.float32, 2)
     _check(q, "latent_prepare.q", None, 2)
     _check(gain, "latent_prepare.gain", torch.float32, 1)
@@ -907,10 +914,10 @@ def latent_prepare(pages, q_eff, down, q, gain, inv_freq, positions, token_item,
         raise KernelError("latent_prepare: sizes do not agree")
     if not pages.is_contiguous() or pages.numel() % (page_size * row) != 0 or not block_table.is_contiguous():
         raise KernelError("latent_prepare: the pages do not hold whole pages of rows of rank + rot")
-    _latent_prepare(pages.data_ptr(), q_eff.data_ptr(), down.data_ptr(), q.data_ptr(), q.stride(0), gain.data_ptr(),
+    _latent_prepare(pages.data_ptr(), q_eff.data_ptr(), down.data_ptr() if down.numel() else None, q.data_ptr(), q.stride(0), gain.data_ptr(),
                     inv_freq.data_ptr(), positions.data_ptr(), token_item.data_ptr(), block_table.data_ptr(),
                     block_table.shape[1], page_size, n, rank, rot, rot_dims, heads, dim, float(eps), int(bool(writes)),
-                    dtype_code(q.dtype), _stream())
+                    ROTARY_LAYOUTS[layout], dtype_code(q.dtype), _stream())
 
 
 _head_linear = Function("sequence", "mllm_sequence_head_linear", [P, P, P, I, I, I, I, L, L, L, L, I, I, I, P])
@@ -932,10 +939,11 @@ def head_linear(out, a, w, heads, a_head, o_head):
     return out
 
 
-_latent_attention = Function("sequence", "mllm_sequence_latent_attention", [P, P, P, P, I, P, P, I, I, I, I, I, F, I, P])
+_latent_attention = Function("sequence", "mllm_sequence_latent_attention", [P, P, P, P, I, P, P, I, I, I, I, I, F, I, I, P])
 
 
-def latent_attention_plain(out, q_eff, pages, block_table, positions, token_item, heads, rank, rot, page_size, scale):
+def latent_attention_plain(out, q_eff, pages, block_table, positions, token_item, heads, rank, rot, page_size, scale,
+                           window=0):
     """Causal attention of every token of the step over its request's cached rows [rank + rot]:
     score = q_eff[t, head] . row * scale, value = the row's first ``rank`` entries;
     out [T, heads * rank] in 32-bit."""
@@ -949,7 +957,7 @@ def latent_attention_plain(out, q_eff, pages, block_table, positions, token_item
         raise KernelError("latent_attention: sizes do not agree")
     _latent_attention(out.data_ptr(), q_eff.data_ptr(), pages.data_ptr(), block_table.data_ptr(), block_table.shape[1],
                       positions.data_ptr(), token_item.data_ptr(), n, heads, rank, rot, page_size, float(scale),
-                      dtype_code(pages.dtype), _stream())
+                      int(window or 0), dtype_code(pages.dtype), _stream())
     return out
 
 
@@ -957,7 +965,7 @@ class _LatentTiledParams(ctypes.Structure):
     _fields_ = [("out", P), ("part_out", P), ("part_ml", P), ("q_eff", P), ("pages", P), ("block_table", P),
                 ("positions", P), ("token_item", P), ("tiles", P), ("max_blocks", I), ("page_size", I), ("n_tokens", I),
                 ("heads", I), ("rank", I), ("rot", I), ("TQ", I), ("HB", I), ("parts", I),
-                ("scale", F), ("out_bf16", I), ("key_buffers", I)]
+                ("scale", F), ("out_bf16", I), ("key_buffers", I), ("window", I)]
 
 
 _latent_attention_tiled = Function("sequence", "mllm_sequence_latent_attention_tiled",
@@ -982,7 +990,7 @@ def latent_heads_per_block(heads: int) -> int:
 
 
 def latent_attention_tiled(out, q_eff, pages, block_table, positions, token_item, heads, rank, rot, page_size, scale,
-                           tiles=None, n_tiles=0, parts=1, scratch=None):
+                           tiles=None, n_tiles=0, parts=1, scratch=None, window=0):
     """``latent_attention_plain`` in tiles of 32 query rows that share their keys.  With ``tiles``
     (the step's work list, device int32 records of 8, ``n_tiles`` of them) for prompt portions;
     without, for single tokens, the keys of each in ``parts`` runs (the token's context length over
@@ -1006,6 +1014,7 @@ def latent_attention_tiled(out, q_eff, pages, block_table, positions, token_item
     params.max_blocks, params.page_size, params.n_tokens = block_table.shape[1], page_size, n
     params.heads, params.rank, params.rot, params.scale = heads, rank, rot, float(scale)
     params.out_bf16 = int(out.dtype == torch.bfloat16)
+    params.window = int(window or 0)           # (> 0: a query sees the last ``window`` positions only)
     if tiles is not None:
         _check(tiles, "latent_attention.tiles", torch.int32)
         if tiles.numel() < ATTENTION_TILE_RECORD * n_tiles or parts != 1:
@@ -1176,7 +1185,7 @@ def rotary_store(qkv, k_off, v_off, heads, kv_heads, dim, vdim, rot_dims, inv_fr
 
 
 _capped_attention = Function("hybrid", "mllm_hybrid_capped_attention",
-                             [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, I, F, F, I, I, I, P])
+                             [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, I, F, F, I, I, P, L, I, I, P])
 
 
 def capped_attention_tiled_takes(dim, vdim, dtype=torch.bfloat16) -> bool:
@@ -1189,11 +1198,14 @@ def capped_attention_tiled_takes(dim, vdim, dtype=torch.bfloat16) -> bool:
 
 
 def capped_attention(out, q, k_pages, v_pages, block_table, positions, token_item, n_heads, n_kv_heads, dim, vdim,
-                     page_size, scale, cap=0.0, window=0, tiled=False):
+                     page_size, scale, cap=0.0, window=0, tiled=False, chunk=0, gate=None):
     """Causal attention of every token of the step over its request's pages, keys of ``dim`` and
     values of ``vdim`` entries per head, score = cap * tanh(q . k * scale / cap) (``cap`` 0: no cap);
-    scores, weights and the weighted sum in 32-bit.  ``tiled``: consecutive tokens of a request share
-    the cached rows they read (for steps with prompt portions)."""
+    scores, weights and the weighted sum in 32-bit.  ``window`` > 0: the last ``window`` positions only;
+    ``chunk`` > 0: only keys of the query's own block of ``chunk`` positions (blocks counted from
+    position 0).  ``gate`` fp32 [T, >= heads]: head h's result is multiplied by sigmoid(gate[t, h]).
+    ``tiled``: consecutive tokens of a request share the cached rows they read (for steps with prompt
+    portions)."""
     _check(out, "capped_attention.out", q.dtype, 2)
     _check(q, "capped_attention.q", None, 2)
     _check(k_pages, "capped_attention.k_pages", q.dtype)
@@ -1204,11 +1216,38 @@ def capped_attention(out, q, k_pages, v_pages, block_table, positions, token_ite
         raise KernelError("capped_attention: q / out do not have heads * size columns")
     if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous():
         raise KernelError("capped_attention: pages and block table must be contiguous")
+    if gate is not None:
+        _check(gate, "capped_attention.gate", torch.float32, 2)
+        if gate.shape[0] < n or gate.shape[1] < n_heads or gate.stride(1) != 1:
+            raise KernelError("capped_attention: one gate per token and head")
     _capped_attention(out.data_ptr(), out.stride(0), q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
                       block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), token_item.data_ptr(), n, n_heads,
-                      n_kv_heads, dim, vdim, page_size, float(scale), float(cap or 0.0), int(window or 0), int(bool(tiled)),
-                      dtype_code(q.dtype), _stream())
+                      n_kv_heads, dim, vdim, page_size, float(scale), float(cap or 0.0), int(window or 0), int(chunk or 0),
+                      _ptr(gate), gate.stride(0) if gate is not None else 0, int(bool(tiled)), dtype_code(q.dtype), _stream())
     return out
+
+
+_head_norm_store = Function("hybrid", "mllm_hybrid_head_norm_store",
+                            [P, L, I, I, I, I, I, I, F, P, P, P, I, I, P, P, I, I, I, P])
+
+
+def head_norm_store(qkv, k_off, v_off, heads, kv_heads, dim, vdim, eps, positions, token_item, block_table, page_size,
+                    k_pages, v_pages, writes=True):
+    """Rows of ``qkv`` hold [q | k | v] (k from column ``k_off``, v from ``v_off``).  Every query and
+    key head is divided by its root mean square, x / sqrt(mean(x^2) + eps), in place (``eps`` < 0: left as
+    they are); the keys and the values go to the token's place in the pages."""
+    _check(qkv, "head_norm_store.qkv", None, 2)
+    _check(k_pages, "head_norm_store.k_pages", qkv.dtype)
+    _check(v_pages, "head_norm_store.v_pages", qkv.dtype)
+    _check(block_table, "head_norm_store.block_table", torch.int32, 2)
+    if (heads * dim > k_off or k_off + kv_heads * dim > v_off or v_off + kv_heads * vdim > qkv.shape[1] or qkv.stride(1) != 1):
+        raise KernelError("head_norm_store: sizes do not agree")
+    if (not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous()
+            or k_pages.numel() % (page_size * kv_heads * dim) != 0 or v_pages.numel() % (page_size * kv_heads * vdim) != 0):
+        raise KernelError("head_norm_store: the pages do not hold whole pages of these rows")
+    _head_norm_store(qkv.data_ptr(), qkv.stride(0), k_off, v_off, heads, kv_heads, dim, vdim, float(eps), positions.data_ptr(),
+                     token_item.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, k_pages.data_ptr(),
+                     v_pages.data_ptr(), int(bool(writes)), qkv.shape[0], dtype_code(qkv.dtype), _stream())
 
 
 class _RecurrenceParams(ctypes.Structure):
@@ -1216,20 +1255,22 @@ class _RecurrenceParams(ctypes.Structure):
                 ("gate_a", P), ("gate_b", P), ("ld_gate_a", L), ("ld_gate_b", L), ("log_rate", P), ("step_bias", P),
                 ("skip", P), ("state", P), ("state_stride", L), ("item_slot", P), ("item_offset", P), ("item_count", P),
                 ("heads", I), ("qk_heads", I), ("dim", I), ("vdim", I), ("q_scale", F), ("delta", I), ("unit_norm", I),
-                ("writes", I)]
+                ("writes", I), ("channel_decay", I)]
 
 
 _linear_recurrence = Function("hybrid", "mllm_hybrid_linear_recurrence", [ctypes.POINTER(_RecurrenceParams), I, I, I, P])
 
 
 def linear_recurrence(out, q, k, v, gate_a, gate_b, log_rate, step_bias, state, item_slot, item_offset, item_count, heads,
-                      qk_heads, dim, vdim, delta, unit_norm=False, q_scale=1.0, skip=None, writes=True):
+                      qk_heads, dim, vdim, delta, unit_norm=False, q_scale=1.0, skip=None, writes=True, channel_decay=False):
     """Per entry, its tokens in order, per head with the state S [dim, vdim] (fp32, in ``state``
     [slots, heads * dim * vdim]): step = softplus(gate_a[t, h] + step_bias[h]), a = exp(-exp(log_rate[h]) * step);
     without ``delta``: u = step * v; with: u = sigmoid(gate_b[t, h]) * (v - (a S)^T k); S <- a S + k u^T;
     out[t, h] = S^T q (+ skip[h] * v).  q, k [T, qk_heads * dim] (head h reads h // (heads // qk_heads)),
     v [T, heads * vdim], any row stride; gates fp32 [T, heads]; out fp32 [T, heads * vdim].  ``unit_norm``:
-    q and k are divided by sqrt(sum(x^2) + 1e-6) per head first; q is multiplied by ``q_scale``."""
+    q and k are divided by sqrt(sum(x^2) + 1e-6) per head first; q is multiplied by ``q_scale``.
+    ``channel_decay``: one decay per key channel, a[i] = exp(-exp(log_rate[h]) * softplus(gate_a[t, h, i] + step_bias[h, i]))
+    with gate_a [T, heads * dim] and step_bias [heads * dim]; row i of S is multiplied by a[i] before it is read."""
     _check(out, "linear_recurrence.out", torch.float32, 2)
     for name, t in (("q", q), ("k", k), ("v", v)):
         _check(t, f"linear_recurrence.{name}", q.dtype, 2)
@@ -1240,7 +1281,8 @@ def linear_recurrence(out, q, k, v, gate_a, gate_b, log_rate, step_bias, state, 
     n = q.shape[0]
     if (q.shape[1] != qk_heads * dim or k.shape[1] != qk_heads * dim or v.shape[1] != heads * vdim
             or out.shape != (n, heads * vdim) or state.shape[1] != heads * dim * vdim or state.stride(1) != 1
-            or gate_a.shape[1] < heads or log_rate.shape[0] != heads or step_bias.shape[0] != heads):
+            or gate_a.shape[1] < heads * (dim if channel_decay else 1) or log_rate.shape[0] != heads
+            or step_bias.shape[0] != heads * (dim if channel_decay else 1) or gate_a.stride(1) != 1):
         raise KernelError("linear_recurrence: sizes do not agree")
     params = _RecurrenceParams()
     params.out, params.ld_out = out.data_ptr(), out.stride(0)
@@ -1260,6 +1302,7 @@ def linear_recurrence(out, q, k, v, gate_a, gate_b, log_rate, step_bias, state, 
     params.item_slot, params.item_offset, params.item_count = item_slot.data_ptr(), item_offset.data_ptr(), item_count.data_ptr()
     params.heads, params.qk_heads, params.dim, params.vdim = heads, qk_heads, dim, vdim
     params.q_scale, params.delta, params.unit_norm, params.writes = float(q_scale), int(bool(delta)), int(bool(unit_norm)), int(bool(writes))
+    params.channel_decay = int(bool(channel_decay))
     _linear_recurrence(ctypes.byref(params), item_count.shape[0], n, dtype_code(q.dtype), _stream())
     return out
 
@@ -1343,3 +1386,67 @@ def scaled_add(x, u, a, v=None, b=0.0):
             raise KernelError("scaled_add: v must be contiguous and of x's shape")
     _scaled_add(x.data_ptr(), u.data_ptr(), float(a), _ptr(v), float(b), x.numel(), _stream())
     return x
+
+
+# ---- residual streams (hyper-connections) and gated feed-forwards --------------------------------------
+
+_streams_fill = Function("streams", "mllm_streams_fill", [P, P, I, I, I, P])
+_streams_step = Function("streams", "mllm_streams_step", [P, P, L, P, P, I, P, P, L, P, L, P, F, I, I, I, I, P])
+_gated_act = Function("streams", "mllm_streams_gated_act", [P, L, P, L, I, I, I, I, P])
+MAX_STREAMS = 8
+GATED_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "none": 2}
+
+
+def streams_fill(streams, hidden):
+    """Every stream of ``streams`` [T, s, width] (fp32) becomes the token's row of ``hidden`` [T, width]."""
+    _check(streams, "streams_fill.streams", torch.float32, 3)
+    _check(hidden, "streams_fill.hidden", torch.float32, 2)
+    n, count, width = streams.shape
+    if not streams.is_contiguous() or not hidden.is_contiguous() or hidden.shape != (n, width):
+        raise KernelError("streams_fill: sizes do not agree")
+    _streams_fill(streams.data_ptr(), hidden.data_ptr(), count, width, n, _stream())
+    return streams
+
+
+def streams_step(streams, y=None, mix=None, w_out=None, read=False, w_in=None, u_out=None, normed=None, gain=None, eps=0.0):
+    """One pass over ``streams`` [T, s, width] (fp32, changed in place).  With ``y`` [T, width] (fp32), a
+    sublayer's result: x_t <- sum_s mix[s, t] x_s + w_out[t] y for all streams at once.  With ``read``: the
+    read-out u = sum_s w_in[s] x_s of the streams as they then are (``w_in`` None: their plain sum) goes to
+    ``u_out`` (fp32) and / or, divided by its root mean square (eps inside the root) and times ``gain``, to
+    ``normed`` (float32 or bfloat16)."""
+    _check(streams, "streams_step.streams", torch.float32, 3)
+    n, count, width = streams.shape
+    if not streams.is_contiguous() or count > MAX_STREAMS:
+        raise KernelError(f"streams_step: contiguous streams, at most {MAX_STREAMS}")
+    if y is not None:
+        _check(y, "streams_step.y", torch.float32, 2)
+        _check(mix, "streams_step.mix", torch.float32, 2)
+        _check(w_out, "streams_step.w_out", torch.float32, 1)
+        if y.shape != (n, width) or y.stride(1) != 1 or tuple(mix.shape) != (count, count) or not mix.is_contiguous() or w_out.shape[0] != count:
+            raise KernelError("streams_step: the result or the mixing weights have another shape")
+    for name, t, dims in (("w_in", w_in, 1), ("u_out", u_out, 2), ("gain", gain, 1)):
+        if t is not None:
+            _check(t, f"streams_step.{name}", torch.float32, dims)
+    if normed is not None:
+        _check(normed, "streams_step.normed", None, 2)
+        if gain is None or gain.shape[0] != width or normed.shape != (n, width) or normed.stride(1) != 1 or not read:
+            raise KernelError("streams_step: the normed read-out needs a gain of the width")
+    if (w_in is not None and w_in.shape[0] != count) or (u_out is not None and (u_out.shape != (n, width) or u_out.stride(1) != 1)):
+        raise KernelError("streams_step: the read-out's weights or result have another shape")
+    _streams_step(streams.data_ptr(), _ptr(y), y.stride(0) if y is not None else 0, _ptr(mix), _ptr(w_out), int(bool(read)),
+                  _ptr(w_in), _ptr(u_out), u_out.stride(0) if u_out is not None else 0, _ptr(normed),
+                  normed.stride(0) if normed is not None else 0, _ptr(gain), float(eps), count, width, n,
+                  dtype_code(normed.dtype) if normed is not None else DT_F32, _stream())
+    return streams
+
+
+def gated_act(out, gu, activation="silu"):
+    """out[t, f] = act(gu[t, f]) * gu[t, inner + f]: ``gu`` [T, 2 * inner] holds a product's gate and up halves."""
+    _check(out, "gated_act.out", gu.dtype, 2)
+    _check(gu, "gated_act.gu", None, 2)
+    n, inner = out.shape
+    if gu.shape != (n, 2 * inner) or gu.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gated_act: the product holds two halves of the output's width")
+    _gated_act(out.data_ptr(), out.stride(0), gu.data_ptr(), gu.stride(0), inner, GATED_ACTIVATIONS[activation], n,
+               dtype_code(gu.dtype), _stream())
+    return out

@@ -2,7 +2,7 @@
 built-in kinds; ``register_part`` / ``register_arrangement`` add others."""
 
 from . import (attention, block, depth, embedding, experts, filter, latent_attention, matrix_memory, mlp, norm,  # noqa
-               recurrence, rotary)  # noqa: F401  (register themselves)
+               recurrence, rotary, streams)  # noqa: F401  (register themselves)
 from .base import (Arrangement, Embedding, FeedForward, Head, InputFilter, Mixer, Norm, Part, PositionEncoding,
                    build_part, get_arrangement, register_arrangement, register_part)
 from .spec import (FixedState, LayerSpec, ModelSpec, NoCache, PagedKV, PartSpec, RunEntry, WeightSpec)

@@ -195,5 +195,88 @@ class FilteredAttention(Mixer):
         ctx.kernels.scaled_add(hidden, self.compute(ctx, x, cache), 1.0)
 
 
+class GatedAttention(Mixer):
+    """Causal attention without positions in its scores: ``q = W_q x + b_q`` and likewise k, v (one product
+    over the stacked matrices; ``bias=False``: no biases); with ``head_norm_eps`` every query and key head is
+    divided by its root mean square, ``x / sqrt(mean(x^2) + eps)``, without a gain; ``score = q . k * scale``
+    over the keys the mask shows: positions <= the query's, of those the last ``window`` if given, and of
+    those the ones in the query's own block of ``chunk`` positions if given (blocks are counted from
+    position 0 of the sequence); softmax and the weighted sum in 32-bit; query head h reads key/value
+    head ``h // (heads / kv_heads)``.  With ``gate`` head h's result is multiplied by
+    ``sigmoid(w_g[h] . x)`` (one number per token and head, read off the same input); then ``W_o``
+    (``out_bias``: with its bias).  The normed keys and the values are what the pages hold."""
+
+    graph_safe = True
+
+    def __init__(self, prefix, width: int, n_heads: int, n_kv_heads: int, key_size: int, value_size: int,
+                 score_scale: float, head_norm_eps: float | None = None, window: int | None = None, chunk: int | None = None,
+                 gate: bool = False, bias: bool = True, out_bias: bool = False, names: dict | None = None):
+        super().__init__(prefix)
+        self.width, self.n_heads, self.n_kv_heads = int(width), int(n_heads), int(n_kv_heads)
+        self.dim, self.vdim, self.score_scale = int(key_size), int(value_size), float(score_scale)
+        if min(self.n_heads, self.n_kv_heads, self.dim, self.vdim) <= 0 or self.n_heads % self.n_kv_heads != 0:
+            raise ValueError(f"{prefix}: {self.n_heads} heads are not a positive multiple of {self.n_kv_heads} key/value heads")
+        self.head_norm_eps = float(head_norm_eps) if head_norm_eps is not None else None
+        self.window, self.chunk = (int(window) if window else None), (int(chunk) if chunk else None)
+        self.gate, self.bias, self.out_bias = bool(gate), bool(bias), bool(out_bias)
+        self.names = dict(q="q", k="k", v="v", o="o", g="g", bias=".b")
+        self.names.update(names or {})
+        self.q_width, self.k_width, self.v_width = self.n_heads * self.dim, self.n_kv_heads * self.dim, self.n_kv_heads * self.vdim
+        self.qkv_width = self.q_width + self.k_width + self.v_width
+
+    def weight_specs(self):
+        n = self.names
+        specs = []
+        for name, rows in ((n["q"], self.q_width), (n["k"], self.k_width), (n["v"], self.v_width)):
+            specs.append(WeightSpec(self.full_name(name), (rows, self.width)))
+            if self.bias:
+                specs.append(WeightSpec(self.full_name(name + n["bias"]), (rows,), role="vector", init="bias"))
+        if self.gate:
+            specs.append(WeightSpec(self.full_name(n["g"]), (self.n_heads, self.width)))
+        specs.append(WeightSpec(self.full_name(n["o"]), (self.width, self.n_heads * self.vdim), init="residual_matrix"))
+        if self.out_bias:
+            specs.append(WeightSpec(self.full_name(n["o"] + n["bias"]), (self.width,), role="vector", init="bias"))
+        return specs
+
+    def cache_need(self):
+        return PagedKV(self.n_kv_heads, self.dim, self.window, value_size=self.vdim)
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        n = self.names
+        three = (n["q"], n["k"], n["v"])
+        self.stacked = torch.cat([self.w(name) for name in three]).contiguous()
+        self.stacked_bias = torch.cat([self.w(name + n["bias"]) for name in three]).contiguous() if self.bias else None
+        if self.gate:
+            # rows of zeros up to the least a tensor-core tile takes; the gate leaves its product in 32-bit
+            gate = self.w(n["g"])
+            self.gate_matrix = gate.contiguous()
+            if gate.shape[0] < 16:
+                self.gate_matrix = torch.zeros((16, gate.shape[1]), dtype=gate.dtype, device=gate.device)
+                self.gate_matrix[:gate.shape[0]] = gate
+
+    def compute(self, ctx, x, cache):
+        k, n = ctx.kernels, x.shape[0]
+        qkv = ctx.buffer("qkv", (n, self.qkv_width), ctx.act_dtype)
+        k.linear(ctx, qkv, x, self.stacked, self.stacked_bias)
+        gate = None
+        if self.gate:
+            gate = ctx.buffer("attention_gate", (n, self.gate_matrix.shape[0]), torch.float32)
+            k.linear(ctx, gate, x, self.gate_matrix)
+        k.head_norm_store(ctx, cache, qkv, self.q_width, self.q_width + self.k_width, self.n_heads, self.n_kv_heads, self.dim,
+                          self.vdim, self.head_norm_eps)
+        mixed = ctx.buffer("attn_out", (n, self.n_heads * self.vdim), ctx.act_dtype)
+        k.capped_attention(ctx, mixed, qkv[:, :self.q_width], cache, self.n_heads, self.n_kv_heads, self.dim, self.vdim,
+                           self.score_scale, 0.0, self.window or 0, chunk=self.chunk or 0, gate=gate)
+        out = ctx.buffer("mixer_out", (n, self.width), torch.float32)
+        k.linear(ctx, out, mixed, self.w(self.names["o"]),
+                 self.w(self.names["o"] + self.names["bias"]) if self.out_bias else None)
+        return out
+
+    def forward(self, ctx, x, hidden, cache):
+        ctx.kernels.scaled_add(hidden, self.compute(ctx, x, cache), 1.0)
+
+
 register_part("causal_self_attention", CausalSelfAttention)
 register_part("filtered_attention", FilteredAttention)
+register_part("gated_attention", GatedAttention)

@@ -10,6 +10,11 @@ residual stream stays 32-bit; mixers and feed-forwards add into it in place.
 x by a weighted sum of all layer results so far.  The input filter (a short convolution, say) and
 the feed-forward are optional roles; the mixer and the feed-forward hand over their output itself
 (``compute``), and the outer norm adds it onto the stream (``add_normed``).
+
+"hyper_connections" is the pre-norm block over several residual streams (``ctx.streams``; see
+``parts.streams``): each sublayer reads a weighted sum of the streams through its norm and writes
+its result back onto all of them through a mixing matrix.  ``hidden`` is not touched; the model
+sums the streams after its last layer.
 """
 
 from __future__ import annotations
@@ -62,5 +67,25 @@ class SandwichNorm(Arrangement):
             parts["depth_mix"].forward(ctx, hidden)
 
 
+class HyperConnections(Arrangement):
+    roles = ("streams_1", "norm_1", "mixer")
+    optional_roles = ("streams_2", "norm_2", "feed_forward")     # a layer may have no feed-forward
+
+    def run(self, ctx, parts, hidden, cache):
+        first = parts["streams_1"]
+        x = first.read(ctx, parts["norm_1"], tag="norm_1")
+        if getattr(cache, "kind", "none") == "composite":
+            cache = cache.sub("mixer")
+        y = parts["mixer"].compute(ctx, x, cache)
+        if "feed_forward" not in parts:
+            first.write(ctx, y)
+            return
+        # the mixer's result goes onto the streams and the feed-forward's input comes off them in one pass
+        second = parts["streams_2"]
+        x = first.write_then_read(ctx, y, second, parts["norm_2"], tag="norm_2")
+        second.write(ctx, parts["feed_forward"].compute(ctx, x))
+
+
 register_arrangement("pre_norm", PreNorm())
+register_arrangement("hyper_connections", HyperConnections())
 register_arrangement("sandwich_norm", SandwichNorm())

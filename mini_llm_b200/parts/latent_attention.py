@@ -13,8 +13,15 @@ in 32-bit, attends over the cached rows (score = effective query . row * scale, 
 first ``rank`` entries; softmax in 32-bit), and expands the result with U_v[h].  A prompt portion
 and a single decoded token take the same path, and no key or value per head is ever stored.
 
-Rotary positions use the interleaved layout: among the first ``rotary_dims`` entries of the
-rotated part, entries 2i and 2i+1 form a pair that turns by ``position * base^(-2i/rotary_dims)``.
+Rotary positions: among the first ``rotary_dims`` entries of the rotated part, pair i turns by
+``position * base^(-2i/rotary_dims)``; ``rotary_layout`` says which entries form pair i: 2i and 2i+1
+("interleaved") or i and i + rotary_dims/2 ("half").
+
+Options: ``window``: a query sees only the last ``window`` positions (itself included); the cache then
+keeps ``keep`` >= ``window`` positions (``keep``: the widest window of all entries that read these
+rows).  ``query_rank``: the queries go through a latent of their own, ``q = W_uq rms(W_dq x) * g_q``.
+``own_rows=False``: the part has no down projection and stores nothing; it attends over the rows that
+another run entry stores (``RunEntry.cache_of``), with its own expansions, queries and mask.
 """
 
 from __future__ import annotations
@@ -32,7 +39,10 @@ class LatentAttention(Mixer):
     def __init__(self, prefix, width: int, n_heads: int, head_size: int, rotated_size: int, value_size: int,
                  latent_size: int, score_scale: float, rotary_base: float, rotary_dims: int, eps: float,
                  q_name: str = "q", down_name: str = "dkv", latent_norm_name: str = "dkv.norm",
-                 key_up_name: str = "uk", value_up_name: str = "uv", out_name: str = "o"):
+                 key_up_name: str = "uk", value_up_name: str = "uv", out_name: str = "o", window: int | None = None,
+                 keep: int | None = None, rotary_layout: str = "interleaved", query_rank: int | None = None,
+                 query_down_name: str = "dq", query_norm_name: str = "dq.norm", query_up_name: str = "uq",
+                 own_rows: bool = True):
         super().__init__(prefix)
         self.width, self.n_heads = int(width), int(n_heads)
         self.dim, self.rot, self.vdim, self.rank = int(head_size), int(rotated_size), int(value_size), int(latent_size)
@@ -43,22 +53,36 @@ class LatentAttention(Mixer):
                              f"(an even number, at most the part)")
         if min(self.n_heads, self.dim, self.vdim, self.rank) <= 0:
             raise ValueError(f"{prefix}: heads, head size, value size and latent size must be positive")
-        self.names = dict(q=q_name, down=down_name, norm=latent_norm_name, uk=key_up_name, uv=value_up_name, o=out_name)
+        self.names = dict(q=q_name, down=down_name, norm=latent_norm_name, uk=key_up_name, uv=value_up_name, o=out_name,
+                          dq=query_down_name, dq_norm=query_norm_name, uq=query_up_name)
         self.row = self.rank + self.rot
+        self.window = int(window) if window else None
+        self.keep = max(int(keep), self.window) if keep and self.window else self.window
+        if rotary_layout not in ("interleaved", "half"):
+            raise ValueError(f"{prefix}: unknown layout of the rotated pairs '{rotary_layout}' (known: half, interleaved)")
+        self.rotary_layout = rotary_layout
+        self.query_rank = int(query_rank) if query_rank else None
+        self.own_rows = bool(own_rows)
 
     def weight_specs(self):
         n, h = self.names, self.n_heads
-        return [
-            WeightSpec(self.full_name(n["q"]), (h * (self.dim + self.rot), self.width)),
-            WeightSpec(self.full_name(n["down"]), (self.row, self.width)),
-            WeightSpec(self.full_name(n["norm"]), (self.rank,), role="vector", init="gain"),
+        if self.query_rank:
+            specs = [WeightSpec(self.full_name(n["dq"]), (self.query_rank, self.width)),
+                     WeightSpec(self.full_name(n["dq_norm"]), (self.query_rank,), role="vector", init="gain"),
+                     WeightSpec(self.full_name(n["uq"]), (h * (self.dim + self.rot), self.query_rank))]
+        else:
+            specs = [WeightSpec(self.full_name(n["q"]), (h * (self.dim + self.rot), self.width))]
+        if self.own_rows:
+            specs += [WeightSpec(self.full_name(n["down"]), (self.row, self.width)),
+                      WeightSpec(self.full_name(n["norm"]), (self.rank,), role="vector", init="gain")]
+        return specs + [
             WeightSpec(self.full_name(n["uk"]), (h * self.dim, self.rank)),
             WeightSpec(self.full_name(n["uv"]), (h * self.vdim, self.rank)),
             WeightSpec(self.full_name(n["o"]), (self.width, h * self.vdim), init="residual_matrix"),
         ]
 
     def cache_need(self):
-        return PagedKV(1, self.row, None, has_values=False)
+        return PagedKV(1, self.row, self.keep, has_values=False)
 
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
@@ -72,19 +96,33 @@ class LatentAttention(Mixer):
         self.inv_freq = (torch.tensor(self.rotary_base, dtype=torch.float64) ** exponent).to(uk.device)
         if half == 0:
             self.inv_freq = torch.zeros(1, dtype=torch.float64, device=uk.device)
+        self._no_gain = torch.ones(self.rank, dtype=torch.float32, device=uk.device)
 
     def compute(self, ctx, x, cache):
-        k, n, h = ctx.kernels, x.shape[0], self.n_heads
+        k, n, h, names = ctx.kernels, x.shape[0], self.n_heads, self.names
+        if self.own_rows != bool(cache.writes):
+            raise RuntimeError(f"{self.prefix}: a part {'with' if self.own_rows else 'without'} a down projection got a cache "
+                               f"it may {'not ' if self.own_rows else ''}store into (RunEntry.cache_of)")
         q = ctx.buffer("latent_q", (n, h * (self.dim + self.rot)), ctx.act_dtype)
-        k.linear(ctx, q, x, self.w(self.names["q"]))
-        down = ctx.buffer("latent_down", (n, self.row), torch.float32)
-        k.linear(ctx, down, x, self.w(self.names["down"]))
+        if self.query_rank:
+            # the query's own latent: its norm reads the product in 32-bit
+            thin = ctx.buffer("latent_q_down", (n, self.query_rank), torch.float32)
+            k.linear(ctx, thin, x, self.w(names["dq"]))
+            normed = ctx.buffer("latent_q_normed", (n, self.query_rank), ctx.act_dtype)
+            k.grouped_rms_norm(normed, thin, self.w(names["dq_norm"]), 1, self.eps)
+            k.linear(ctx, q, normed, self.w(names["uq"]))
+        else:
+            k.linear(ctx, q, x, self.w(names["q"]))
+        down = None
+        if self.own_rows:
+            down = ctx.buffer("latent_down", (n, self.row), torch.float32)
+            k.linear(ctx, down, x, self.w(names["down"]))
         q_eff = ctx.buffer("latent_q_eff", (n, h * self.row), torch.float32)
-        k.latent_prepare(ctx, cache, q_eff, down, q, self.w(self.names["norm"]), self.inv_freq, self.rank, self.rot,
-                         self.rotary_dims, h, self.dim, self.eps)
+        k.latent_prepare(ctx, cache, q_eff, down, q, self.w(names["norm"]) if self.own_rows else self._no_gain, self.inv_freq,
+                         self.rank, self.rot, self.rotary_dims, h, self.dim, self.eps, layout=self.rotary_layout)
         k.head_linear(ctx, q_eff, q, self.key_up_t, h, self.dim + self.rot, self.row)
         mixed_latent = ctx.buffer("latent_mixed", (n, h * self.rank), k.latent_mixed_dtype(cache, self.rank, self.rot))
-        k.latent_attention(ctx, mixed_latent, q_eff, cache, h, self.rank, self.rot, self.score_scale)
+        k.latent_attention(ctx, mixed_latent, q_eff, cache, h, self.rank, self.rot, self.score_scale, window=self.window or 0)
         mixed = ctx.buffer("attn_out", (n, h * self.vdim), ctx.act_dtype)
         k.head_linear(ctx, mixed, mixed_latent, self.value_up, h, self.rank, self.vdim)
         out = ctx.buffer("mixer_out", (n, self.width), torch.float32)

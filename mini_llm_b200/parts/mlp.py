@@ -3,7 +3,10 @@ residual stream (engine/src/transformer_block.c:64-71).  The activation is a
 parameter: the tanh form of gelu (engine/include/gelu_math.h:6-11) or the erf
 form (engine/src/gelu.c:5-9), or the square of relu.  Biases are optional, and the tensors'
 names are parameters (``weight_suffix=""`` for files that name a matrix by its layer alone).
-``compute`` returns the output itself, in 32-bit, for arrangements that norm it before the sum."""
+``compute`` returns the output itself, in 32-bit, for arrangements that norm it before the sum.
+
+``gated_mlp``: ``W_down (act(W_gate x + b_gate) * (W_up x + b_up)) + b_down``; gate and up are one
+product over the stacked matrices, the activation and the product of the halves one pass."""
 
 from __future__ import annotations
 
@@ -66,4 +69,54 @@ class DenseMlp(FeedForward):
         return out
 
 
+class GatedMlp(FeedForward):
+    graph_safe = True
+    ACTIVATIONS = ("silu", "gelu_tanh")
+
+    def __init__(self, prefix, width: int, inner: int, activation: str = "silu", bias: bool = True, gate_name: str = "gate",
+                 up_name: str = "up", down_name: str = "down", bias_suffix: str = ".b"):
+        super().__init__(prefix)
+        self.width, self.inner = int(width), int(inner)
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"{prefix}: unknown gate activation '{activation}' (known: {', '.join(self.ACTIVATIONS)})")
+        if min(self.width, self.inner) <= 0:
+            raise ValueError(f"{prefix}: width and inner size must be positive")
+        self.activation, self.bias, self.bias_suffix = activation, bool(bias), bias_suffix
+        self.names = dict(gate=gate_name, up=up_name, down=down_name)
+
+    def weight_specs(self):
+        n = self.names
+        specs = [WeightSpec(self.full_name(n["gate"]), (self.inner, self.width)),
+                 WeightSpec(self.full_name(n["up"]), (self.inner, self.width)),
+                 WeightSpec(self.full_name(n["down"]), (self.width, self.inner), init="residual_matrix")]
+        if self.bias:
+            specs += [WeightSpec(self.full_name(n[key] + self.bias_suffix), (size,), role="vector", init="bias")
+                      for key, size in (("gate", self.inner), ("up", self.inner), ("down", self.width))]
+        return specs
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        n = self.names
+        self.stacked = torch.cat([self.w(n["gate"]), self.w(n["up"])]).contiguous()
+        self.stacked_bias = (torch.cat([self.w(n["gate"] + self.bias_suffix), self.w(n["up"] + self.bias_suffix)]).contiguous()
+                             if self.bias else None)
+        self.down_bias = self.w(n["down"] + self.bias_suffix) if self.bias else None
+
+    def _activated(self, ctx, x):
+        both = ctx.buffer("mlp_gate_up", (x.shape[0], 2 * self.inner), ctx.act_dtype)
+        ctx.kernels.linear(ctx, both, x, self.stacked, self.stacked_bias)
+        act = ctx.buffer("mlp_up", (x.shape[0], self.inner), ctx.act_dtype)
+        ctx.kernels.gated_act(act, both, self.activation)
+        return act
+
+    def forward(self, ctx, x, hidden):
+        ctx.kernels.linear(ctx, hidden, self._activated(ctx, x), self.w(self.names["down"]), self.down_bias, epilogue="add")
+
+    def compute(self, ctx, x):
+        out = ctx.buffer("mlp_out", (x.shape[0], self.width), torch.float32)
+        ctx.kernels.linear(ctx, out, self._activated(ctx, x), self.w(self.names["down"]), self.down_bias)
+        return out
+
+
 register_part("dense_mlp", DenseMlp)
+register_part("gated_mlp", GatedMlp)

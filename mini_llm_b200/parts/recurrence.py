@@ -13,6 +13,11 @@ its own: ``S <- a_t S + k_t u_t^T``, read after the write as ``S^T q_t``.  With
     per group (head h reads group ``h // (heads / groups)``), plus ``D[h] x_t`` on the output; the
     output times ``silu(z)`` is then normed in ``norm_groups`` equal parts, times a gain, then ``W_o``.
 
+``channel_delta_memory``: the gated delta rule with one decay per head and key channel,
+    ``a_t[h, i] = exp(-exp(log_rate[h]) * softplus((W_a2 (W_a1 x_t))[h, i] + step_bias[h, i]))``, which multiplies
+    row i of S before the old state is read; the step's projection is a product of two thin
+    matrices, and so is the output gate, which is ``sigmoid(W_g2 (W_g1 x))``.
+
 State per request (32-bit, in its slot): S [heads, dim, vdim] and the convolution's last
 ``taps - 1`` inputs.  Steps, decays, write gates, unit norms and the recurrence are 32-bit; the
 projections that feed gates and steps leave their product in 32-bit.
@@ -109,6 +114,86 @@ class GatedDeltaMemory(Mixer):
 
     def forward(self, ctx, x, hidden, cache):
         ctx.kernels.scaled_add(hidden, self.compute(ctx, x, cache), 1.0)
+
+
+class ChannelDeltaMemory(GatedDeltaMemory):
+    """``gated_delta_memory`` with a decay per key channel and thin pairs of matrices for the decay's
+    step (``step_rank``) and for the output gate (``gate_rank``, a sigmoid gate).  An inner size of
+    None is read off the stored matrices."""
+
+    def __init__(self, prefix, width: int, n_heads: int, n_qk_heads: int, key_size: int, value_size: int, taps: int,
+                 eps: float, step_rank: int | None = None, gate_rank: int | None = None, names: dict | None = None):
+        more = dict(step_down="a1", step_up="a2", gate_down="g1", gate_up="g2")
+        more.update(names or {})
+        super().__init__(prefix, width, n_heads, n_qk_heads, key_size, value_size, taps, eps, more)
+        self.step_rank = int(step_rank) if step_rank is not None else None
+        self.gate_rank = int(gate_rank) if gate_rank is not None else None
+        if min(self.step_rank or 1, self.gate_rank or 1) <= 0:
+            raise ValueError(f"{prefix}: the thin matrices' inner sizes must be positive")
+
+    def weight_specs(self):
+        n, h = self.names, self.n_heads
+        specs = []
+        for name, rows in ((n["q"], self.qk), (n["k"], self.qk), (n["v"], self.vw)):
+            specs += [WeightSpec(self.full_name(name), (rows, self.width)),
+                      WeightSpec(self.full_name(name + n["taps"]), (rows, self.taps), role="vector", init="matrix")]
+        return specs + [
+            WeightSpec(self.full_name(n["write"]), (h, self.width)),
+            WeightSpec(self.full_name(n["log_rate"]), (h,), role="vector", init="bias"),
+            WeightSpec(self.full_name(n["norm"]), (self.vdim,), role="vector", init="gain"),
+            WeightSpec(self.full_name(n["step_down"]), (self.step_rank, self.width)),
+            WeightSpec(self.full_name(n["step_up"]), (h * self.dim, self.step_rank)),
+            WeightSpec(self.full_name(n["step_bias"]), (h * self.dim,), role="vector", init="bias"),
+            WeightSpec(self.full_name(n["gate_down"]), (self.gate_rank, self.width)),
+            WeightSpec(self.full_name(n["gate_up"]), (self.vw, self.gate_rank)),
+            WeightSpec(self.full_name(n["o"]), (self.width, self.vw), init="residual_matrix"),
+        ]
+
+    def bind(self, tensors, runtime):
+        Mixer.bind(self, tensors, runtime)
+        n = self.names
+        for down, up in (("step_down", "step_up"), ("gate_down", "gate_up")):
+            if self.w(n[down]).shape[0] != self.w(n[up]).shape[1]:
+                raise ValueError(f"{self.full_name(n[down])} has {self.w(n[down]).shape[0]} rows but {self.full_name(n[up])} "
+                                 f"has {self.w(n[up]).shape[1]} columns")
+        self.step_rank, self.gate_rank = self.w(n["step_down"]).shape[0], self.w(n["gate_down"]).shape[0]
+        self.stacked = torch.cat([self.w(n["q"]), self.w(n["k"]), self.w(n["v"])]).contiguous()
+        self.stacked_taps = torch.cat([self.w(name + n["taps"]) for name in (n["q"], n["k"], n["v"])]).contiguous()
+        self.write_matrix = _padded_rows(self.w(n["write"]))
+        self.gain = self.w(n["norm"]).repeat(self.n_heads).contiguous()
+        self._no_state = torch.zeros((1, 0, self.filtered), dtype=torch.float32, device=self.stacked.device)
+
+    def compute(self, ctx, x, cache):
+        k, n, h, names = ctx.kernels, x.shape[0], self.n_heads, self.names
+        projected = ctx.buffer("memory_qkvg", (n, self.filtered), ctx.act_dtype)
+        k.linear(ctx, projected, x, self.stacked)
+        held = cache.of("taps") if self.taps > 1 else None
+        filtered = ctx.buffer("memory_filtered", (n, self.filtered), ctx.act_dtype)
+        k.causal_taps(ctx, filtered, projected, self.stacked_taps,
+                      held.state if held is not None else self._no_state, held.writes if held is not None else False,
+                      identity=False, silu=True)
+        # the thin pairs: the steps stay 32-bit (they enter the recurrence), the output gate is an activation
+        thin = ctx.buffer("memory_step_thin", (n, self.step_rank), ctx.act_dtype)
+        k.linear(ctx, thin, x, self.w(names["step_down"]))
+        steps = ctx.buffer("memory_steps", (n, h * self.dim), torch.float32)
+        k.linear(ctx, steps, thin, self.w(names["step_up"]))
+        thin = ctx.buffer("memory_gate_thin", (n, self.gate_rank), ctx.act_dtype)
+        k.linear(ctx, thin, x, self.w(names["gate_down"]))
+        gate = ctx.buffer("memory_gate", (n, self.vw), ctx.act_dtype)
+        k.linear(ctx, gate, thin, self.w(names["gate_up"]))
+        writes = ctx.buffer("memory_gates", (n, self.write_matrix.shape[0]), torch.float32)
+        k.linear(ctx, writes, x, self.write_matrix)
+        read = ctx.buffer("memory_read", (n, self.vw), torch.float32)
+        state = cache.of("state")
+        k.linear_recurrence(ctx, read, filtered[:, :self.qk], filtered[:, self.qk:2 * self.qk], filtered[:, 2 * self.qk:],
+                            steps, writes[:, :h], self.w(names["log_rate"]), self.w(names["step_bias"]), state.state, h,
+                            self.n_qk_heads, self.dim, self.vdim, delta=True, unit_norm=True, q_scale=self.dim ** -0.5,
+                            writes=state.writes, channel_decay=True)
+        mixed = ctx.buffer("attn_out", (n, self.vw), ctx.act_dtype)
+        k.grouped_rms_norm(mixed, read, self.gain, h, self.eps, gate=gate, gate_mode="sigmoid")
+        out = ctx.buffer("mixer_out", (n, self.width), torch.float32)
+        k.linear(ctx, out, mixed, self.w(names["o"]))
+        return out
 
 
 class StateSpaceDuality(Mixer):
@@ -228,5 +313,6 @@ class ParallelMixers(Mixer):
 
 
 register_part("gated_delta_memory", GatedDeltaMemory)
+register_part("channel_delta_memory", ChannelDeltaMemory)
 register_part("state_space_duality", StateSpaceDuality)
 register_part("parallel_mixers", ParallelMixers)

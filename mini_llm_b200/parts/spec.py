@@ -17,7 +17,8 @@ class WeightSpec:
     """One tensor a part needs from the weights file.
 
     name       name in the file (without any file-level prefix)
-    shape      shape as stored in the file
+    shape      shape as stored in the file; a size of None is whatever the file holds there (the
+               part reads it off the tensor when it is bound)
     role       "matrix" (a matrix-product operand), "table" (rows gathered by
                index, may also be a product operand), "vector" (gain, shift,
                bias: kept in 32-bit), "int_table" (kept as int32)
@@ -88,6 +89,8 @@ class ModelSpec:
     embedding_norm: PartSpec | None = None   # a norm applied to the embedded tokens, in place, before the first layer
     keeps_layer_results: bool = False  # the embedding output and every run entry's result stay at hand for the
                                        # layers' "depth_mix" parts (a weighted sum over all of them)
+    residual_streams: int = 0          # > 0: the residual is that many streams [T, streams, width] (``ctx.streams``), all
+                                       # equal to the embedding output at the start and summed after the last layer
     file_prefixes: tuple = ("",)       # prefixes a weights file may put before every name
     ignored_weights: tuple = ()        # regular expressions of file names that are no parameters
     eos_token_id: int | None = None

@@ -63,6 +63,11 @@ class WeightsError(ValueError):
         super().__init__("\n".join(lines))
 
 
+def shape_fits(stored, declared) -> bool:
+    """Whether a stored shape is the declared one; a declared size of None is given by the file."""
+    return len(stored) == len(declared) and all(want is None or int(got) == int(want) for got, want in zip(stored, declared))
+
+
 def collect_specs(parts) -> dict[str, WeightSpec]:
     """All weight specs of ``parts`` by name.  Two parts may name the same
     tensor (a tied head) if they agree on its shape."""
@@ -136,8 +141,8 @@ def load_weights(model_dir: str, specs: dict, engine_dtype: torch.dtype, device,
                 missing.append(name)
             continue
         stored = file.tensors[mapping[name]]
-        if tuple(stored.shape) != tuple(spec.shape):
-            wrong_shape.append((name, stored.shape, spec.shape))
+        if not shape_fits(tuple(stored.shape), tuple(spec.shape)):
+            wrong_shape.append((name, stored.shape, ["any" if size is None else size for size in spec.shape]))
         if spec.role == "int_table":
             if stored.dtype not in ("I64", "I32", "I16", "I8", "U8"):
                 wrong_dtype.append((name, stored.dtype, "an integer type"))

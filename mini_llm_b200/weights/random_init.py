@@ -58,6 +58,8 @@ def random_tensors(spec, seed: int, recipe: str = "gpt2") -> dict:
             continue
         rng = np.random.default_rng([int(seed) & 0xFFFFFFFF, zlib.crc32(name.encode("utf-8"))])
         shape = tuple(w.shape)
+        if any(size is None for size in shape):
+            raise ValueError(f"tensor '{name}' has a size that only a weights file gives; random weights need it as a parameter")
         if w.role == "int_table":
             tensors[name] = rng.integers(0, 2, size=shape, dtype=np.int32)
         elif recipe == "gpt2":
