@@ -142,7 +142,7 @@ def load_weights(model_dir: str, specs: dict, engine_dtype: torch.dtype, device,
             continue
         stored = file.tensors[mapping[name]]
         if not shape_fits(tuple(stored.shape), tuple(spec.shape)):
-            wrong_shape.append((name, stored.shape, ["any" if size is None else size for size in spec.shape]))
+            wrong_shape.append((name, stored.shape, tuple("any" if size is None else size for size in spec.shape)))
         if spec.role == "int_table":
             if stored.dtype not in ("I64", "I32", "I16", "I8", "U8"):
                 wrong_dtype.append((name, stored.dtype, "an integer type"))
