@@ -64,11 +64,12 @@ def parse_args():
     parser.add_argument("--kernels", action="store_true",
                         help="time single kernels (matrix products at forced tile widths, prompt attention) back to "
                              "back in a replayed graph and print one line each: the tables of profiles/ come from this")
-    parser.add_argument("--compare", default=None, choices=("fuvolix", "sumozen"),
+    parser.add_argument("--compare", default=None, choices=("fuvolix", "sumozen", "lipulorn"),
                         help="fuvolix: prefill and decode of Fuvolix stacks at sizes of real layers (random weights), beside "
                              "GPT-2 of equal width, depth and inner size, and their mixers' kernels alone; sumozen: Sumozen "
                              "stacks beside Fuvolix stacks of equal width, depth and inner size, and its kernels alone; "
-                             "one line each")
+                             "lipulorn: Lipulorn stacks beside Fuvolix stacks of equal width, depth and feed-forward weights, and "
+                             "its kernels alone beside the like kernels of Fuvolix and Sumozen; one line each")
     parser.add_argument("--tokens-out", default=None,
                         help="(--impl reference) write the greedy tokens of the fixed check workload to this file "
                              "and print nothing else")
@@ -667,8 +668,10 @@ def run_reference(args):
 def replayed_us(torch, launch, repeats=12):
     """Microseconds per call of ``launch(i)``, i = 0 .. repeats - 1 (each on operands of its own,
     so that nothing stays in L2 from call to call), captured once and replayed: the best of five."""
+    import gc
     launch(0)
     torch.cuda.synchronize()
+    gc.collect()             # a graph of an earlier call that is freed while this one is captured would end the capture
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
         for i in range(repeats):
@@ -684,6 +687,7 @@ def replayed_us(torch, launch, repeats=12):
         last.record()
         torch.cuda.synchronize()
         best = min(best, first.elapsed_time(last) * 1000.0 / repeats)
+    graph.reset()
     return best
 
 
@@ -1097,6 +1101,217 @@ def run_compare_sumozen(args):
     return 0
 
 
+# Lipulorn stacks beside Fuvolix of equal width and depth: layers in sixes (attention over a latent of its own within a
+# window, attention in blocks, a channel delta memory, then the same three with the latent attention reading the first
+# one's rows), four residual streams, every layer with a gated feed-forward of two thirds of the dense inner size (three
+# matrices instead of two: as many weights).
+LIPULORN_SIZES = {
+    "small": {"width": 768, "layers": 12, "ff": 2048, "streams": 4, "fuvolix": "small", "sumozen": "small",
+              "latent": {"heads": 12, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "q_rank": 384, "window": 512},
+              "attention": {"heads": 12, "kv_heads": 4, "dim": 64, "vdim": 64, "chunk": 512},
+              "delta": {"heads": 6, "kv_heads": 3, "dim": 128, "vdim": 128, "a_rank": 64, "g_rank": 64}},
+    "medium": {"width": 1024, "layers": 24, "ff": 2816, "streams": 4, "fuvolix": "medium", "sumozen": "medium",
+               "latent": {"heads": 16, "dim": 64, "rot_dim": 64, "vdim": 64, "kv_rank": 512, "q_rank": 512, "window": 512},
+               "attention": {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 64, "chunk": 512},
+               "delta": {"heads": 8, "kv_heads": 4, "dim": 128, "vdim": 128, "a_rank": 64, "g_rank": 64}},
+}
+
+
+def lipulorn_config(size: dict, vocab: int) -> dict:
+    lat, att, mem = size["latent"], size["attention"], size["delta"]
+    mlp = {"kind": "dense", "ff": size["ff"]}
+
+    def latent(source):
+        mixer = {key: lat[key] for key in ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank")}
+        mixer.update(scale=(lat["dim"] + lat["rot_dim"]) ** -0.5, mask={"size": lat["window"]},
+                     rot={"base": 10000.0, "dims": lat["rot_dim"]})
+        if source is not None:
+            mixer["kv_from"] = source
+        return {"type": "latent_attention", "mixer": mixer, "mlp": mlp}
+    attention = {"type": "attention", "mlp": mlp,
+                 "mixer": {"heads": att["heads"], "kv_heads": att["kv_heads"], "dim": att["dim"], "vdim": att["vdim"],
+                           "scale": att["dim"] ** -0.5, "mask": {"size": att["chunk"]}}}
+    memory = {"type": "channel_delta", "mlp": mlp, "mixer": dict(mem, conv=4)}
+    layers = []
+    for index in range(size["layers"]):
+        layers.append([latent(None), attention, memory, latent(index - 3), attention, memory][index % 6])
+    return {"architecture": "Lipulorn", "vocab": vocab, "width": size["width"], "streams": size["streams"], "norm": {"eps": 1e-5},
+            "layers": layers}
+
+
+def lipulorn_kernels(torch, size: dict, peak: dict):
+    """Lipulorn's kernels alone, replayed back to back on operands of their own: prompt portions
+    (2 x 1,024 tokens) and single tokens (8 requests at 1,023 cached tokens), each with the work it
+    must do and the fraction of its bound: 32-bit FMA (nominal) where the sums are 32-bit by the
+    design's rule, measured HBM copy bandwidth where streams, state or cache are streamed."""
+    from mini_llm_b200.kernels import ops
+    lines = []
+    page, fma_peak = 64, FP32_FMA_TFLOPS_NOMINAL
+    dev = lambda values: torch.tensor(values, dtype=torch.int32, device="cuda")
+
+    def add(kernel, us, flops=None, bytes_moved=None, **more):
+        line = {"kernel": kernel, "us": round(us, 2), **more}
+        if flops is not None:
+            line.update(tflops=round(flops / us / 1e6, 2), frac_fp32_fma_nominal=round(flops / us / 1e6 / fma_peak, 3))
+        if bytes_moved is not None:
+            line.update(gbs=round(bytes_moved / us / 1e3, 1), frac_hbm_measured=round(bytes_moved / us / 1e3 / peak["hbm_gbs"], 3))
+        lines.append(line)
+
+    def batch(lengths, new):
+        blocks = [-(-n // page) for n in lengths]
+        table = torch.zeros(len(lengths), max(blocks), dtype=torch.int32)
+        at = 0
+        for i, count in enumerate(blocks):
+            table[i, :count] = torch.arange(at, at + count, dtype=torch.int32)
+            at += count
+        starts = [length - count for length, count in zip(lengths, new)]
+        positions = torch.cat([torch.arange(s, s + m) for s, m in zip(starts, new)]).int().cuda()
+        token_item = torch.cat([torch.full((m,), i) for i, m in enumerate(new)]).int().cuda()
+        return table.cuda(), sum(blocks), starts, positions, token_item
+
+    shapes = (("prompts, 2 x 1024", [1024, 1024], [1024, 1024]), ("single tokens, 8 x 1024", [1024] * 8, [1] * 8))
+    # ---- attention over the latent within a window ----
+    lat = size["latent"]
+    heads, rank, rot, window = lat["heads"], lat["kv_rank"], lat["rot_dim"], lat["window"]
+    row = rank + rot
+    for name, lengths, new in shapes:
+        table, n_blocks, starts, positions, token_item = batch(lengths, new)
+        n = sum(new)
+        offsets = [sum(new[:i]) for i in range(len(new))]
+        seen = sum(sum(min(p + 1, window) for p in range(s, s + m)) for s, m in zip(starts, new))     # (query token, key) pairs
+        pages = [torch.randn(n_blocks + 1, page, 1, row, device="cuda").bfloat16() for _ in range(4)]
+        q_eff = torch.randn(n, heads * row, device="cuda")
+        out = torch.empty(n, heads * rank, device="cuda")
+        if len(new) == 2:
+            tiles, _, _ = ops.attention_tiles(offsets, new, starts, split=False)
+            tiles_d = dev(tiles)
+            us = replayed_us(torch, lambda i: ops.latent_attention_tiled(out, q_eff, pages[i % 4], table, positions, token_item, heads,
+                                                                         rank, rot, page, 0.1, tiles=tiles_d, n_tiles=len(tiles), window=window))
+            add(f"latent attention in tiles, window {window}, {name}", us, flops=2.0 * seen * heads * (row + rank), heads=heads, row=row)
+        else:
+            parts = max(1, min(32, 296 // (n * (1 if heads <= 16 else -(-heads // 32)))))
+            scratch = (torch.empty(n * heads * parts * rank, device="cuda"), torch.empty(n * heads * parts * 2, device="cuda"))
+            us = replayed_us(torch, lambda i: ops.latent_attention_tiled(out, q_eff, pages[i % 4], table, positions, token_item, heads,
+                                                                         rank, rot, page, 0.1, parts=parts, scratch=scratch, window=window))
+            add(f"latent attention in parts, window {window}, {name}", us, bytes_moved=seen * row * 2.0, heads=heads, row=row, parts=parts)
+    # ---- attention in blocks of positions, normed heads, a gate per head ----
+    att = size["attention"]
+    heads, kv_heads, dim, vdim, chunk = att["heads"], att["kv_heads"], att["dim"], att["vdim"], att["chunk"]
+    for name, lengths, new in shapes:
+        table, n_blocks, starts, positions, token_item = batch(lengths, new)
+        n = sum(new)
+        seen = sum(sum(p % chunk + 1 for p in range(s, s + m)) for s, m in zip(starts, new))
+        k_pages = [torch.randn(n_blocks + 1, page, kv_heads, dim, device="cuda").bfloat16() for _ in range(4)]
+        v_pages = [torch.randn(n_blocks + 1, page, kv_heads, vdim, device="cuda").bfloat16() for _ in range(4)]
+        qkv = [torch.randn(n, (heads + kv_heads) * dim + kv_heads * vdim, device="cuda").bfloat16() for _ in range(4)]
+        gate = torch.randn(n, 16, device="cuda")
+        out = torch.empty(n, heads * vdim, device="cuda", dtype=torch.bfloat16)
+        us = replayed_us(torch, lambda i: ops.head_norm_store(qkv[i % 4], heads * dim, (heads + kv_heads) * dim, heads, kv_heads, dim, vdim, 1e-5,
+                                                              positions, token_item, table, page, k_pages[i % 4], v_pages[i % 4]))
+        add(f"head norms + cache store, {name}", us, bytes_moved=n * ((2 * heads + 2 * kv_heads) * dim + 2 * kv_heads * vdim) * 2.0)
+        q = qkv[0][:, :heads * dim]
+        if len(new) == 2:
+            us = replayed_us(torch, lambda i: ops.capped_attention(out, q, k_pages[i % 4], v_pages[i % 4], table, positions, token_item,
+                                                                   heads, kv_heads, dim, vdim, page, 0.125, 0.0, 0, tiled=True, chunk=chunk, gate=gate))
+            add(f"gated attention in tiles, blocks of {chunk}, {name}", us, flops=2.0 * seen * heads * (dim + vdim), heads=heads, kv_heads=kv_heads, dim=dim)
+        else:
+            span, reach = 128, table.shape[1] * page
+            spans = -(-reach // span)
+            scratch = (torch.empty(n * heads * spans * dim, device="cuda"), torch.empty(n * heads * spans * 2, device="cuda"),
+                       torch.zeros(n * heads, dtype=torch.int32, device="cuda"))
+            us = replayed_us(torch, lambda i: ops.split_attention(out, q, k_pages[i % 4], v_pages[i % 4], table, positions, token_item,
+                                                                  heads, kv_heads, dim, page, 0.125, 0, span, spans, *scratch,
+                                                                  block=chunk, gate=gate))
+            add(f"gated attention over split keys, blocks of {chunk}, {name}", us, bytes_moved=seen * kv_heads * (dim + vdim) * 2.0,
+                heads=heads, kv_heads=kv_heads, dim=dim)
+            us = replayed_us(torch, lambda i: ops.capped_attention(out, q, k_pages[i % 4], v_pages[i % 4], table, positions, token_item,
+                                                                   heads, kv_heads, dim, vdim, page, 0.125, 0.0, 0, chunk=chunk, gate=gate))
+            add(f"gated attention, one block per (token, head), blocks of {chunk}, {name}", us,
+                bytes_moved=seen * kv_heads * (dim + vdim) * 2.0, heads=heads, kv_heads=kv_heads, dim=dim)
+    # ---- the delta memory with a decay per key channel ----
+    mem = size["delta"]
+    h, qk_heads, kd, vd = mem["heads"], mem["kv_heads"], mem["dim"], mem["vdim"]
+    for name, counts in (("prompts, 2 x 1024", [1024, 1024]), ("single tokens, 8", [1] * 8)):
+        n = sum(counts)
+        projected = [torch.randn(n, 2 * qk_heads * kd + h * vd, device="cuda").bfloat16() for _ in range(4)]
+        states = [torch.zeros(len(counts), h * kd * vd, device="cuda") for _ in range(4)]
+        out = torch.empty(n, h * vd, device="cuda")
+        steps, writes = torch.randn(n, h * kd, device="cuda"), torch.randn(n, 16, device="cuda")
+        rate, bias = torch.zeros(h, device="cuda"), torch.zeros(h * kd, device="cuda")
+        slots, offs, cnts = dev(list(range(len(counts)))), dev([sum(counts[:i]) for i in range(len(counts))]), dev(counts)
+
+        def launch(i):
+            x = projected[i % 4]
+            ops.linear_recurrence(out, x[:, :qk_heads * kd], x[:, qk_heads * kd:2 * qk_heads * kd], x[:, 2 * qk_heads * kd:], steps,
+                                  writes[:, :h], rate, bias, states[i % 4], slots, offs, cnts, h, qk_heads, kd, vd, True,
+                                  unit_norm=True, q_scale=kd ** -0.5, channel_decay=True)
+        us = replayed_us(torch, launch)
+        if len(counts) == 2:
+            add(f"channel delta rule, token by token, {name}", us, flops=2.0 * 4 * kd * vd * h * n, heads=h, dim=kd, vdim=vd)
+        else:
+            add(f"channel delta rule, {name}", us, bytes_moved=2.0 * len(counts) * h * kd * vd * 4, heads=h, dim=kd, vdim=vd)
+    # ---- the residual streams and the gated activation ----
+    width, count, inner = size["width"], size["streams"], size["ff"]
+    for name, n in (("2,048 tokens", 2048), ("8 tokens", 8)):
+        streams = [torch.randn(n, count, width, device="cuda") for _ in range(4)]
+        y = [torch.randn(n, width, device="cuda") for _ in range(4)]
+        normed = torch.empty(n, width, device="cuda", dtype=torch.bfloat16)
+        mix = torch.eye(count, device="cuda").contiguous()
+        w_in, w_out, gain = torch.ones(count, device="cuda"), torch.ones(count, device="cuda"), torch.ones(width, device="cuda")
+        us = replayed_us(torch, lambda i: ops.streams_step(streams[i % 4], y=y[i % 4], mix=mix, w_out=w_out, read=True, w_in=w_in,
+                                                           normed=normed, gain=gain, eps=1e-5))
+        add(f"streams: write, read-out and norm in one pass, {name}", us, bytes_moved=n * width * (8.0 * count + 4 + 2), streams=count)
+        x = [torch.randn(n, width, device="cuda") for _ in range(4)]
+        us = replayed_us(torch, lambda i: ops.grouped_rms_norm(normed, x[i % 4], gain, 1, 1e-5))
+        add(f"one residual: norm alone, {name}", us, bytes_moved=n * width * (4.0 + 2))
+        gu = [torch.randn(n, 2 * inner, device="cuda").bfloat16() for _ in range(4)]
+        act = torch.empty(n, inner, device="cuda", dtype=torch.bfloat16)
+        us = replayed_us(torch, lambda i: ops.gated_act(act, gu[i % 4], "silu"))
+        add(f"gated activation, {name}", us, bytes_moved=n * inner * 6.0, inner=inner)
+    return lines
+
+
+
+
+def run_compare_lipulorn(args):
+    """Lipulorn beside Fuvolix of equal width and depth (and as many feed-forward weights): the prompt step of
+    2,048 tokens (2 x 1,024) and the decode step of ``--batch`` requests at a context of 1,024, in bfloat16,
+    through ``Engine.step``; then the kernels alone: Lipulorn's, and the like kernels of Fuvolix (attention
+    over a latent) and Sumozen (attention with grouped heads, the delta rule).  One JSON line per measurement."""
+    import torch
+    from mini_llm_b200.config import config_from_dict
+    from mini_llm_b200.engine import Engine
+    from mini_llm_b200.weights import write_random_model
+    peak = peaks()
+    context, vocab = 1024, GPT2_SMALL["vocab_size"]
+    for name, size in LIPULORN_SIZES.items():
+        for design in ("lipulorn", "fuvolix"):
+            raw = lipulorn_config(size, vocab) if design == "lipulorn" else fuvolix_config(FUVOLIX_SIZES[size["fuvolix"]], vocab)
+            with tempfile.TemporaryDirectory() as folder:
+                write_random_model(config_from_dict(raw), 0, folder, recipe="gpt2", store_dtype="bfloat16")
+                engine = Engine(folder, dtype="bfloat16", max_requests=16, cache_tokens=16 * context, max_tokens_per_step=2048,
+                                **({"page_size": args.page_size} if args.page_size else {}))
+                prefill_ms = prefill_run(engine, 2, 1024, vocab)
+                decode_ms, launches, _ = decode_run(engine, args.batch, args.steps, args.warmup, context, vocab)
+                print(json.dumps({"design": design, "size": name, "width": size["width"], "layers": size["layers"],
+                                  "inner": size["ff"] if design == "lipulorn" else FUVOLIX_SIZES[size["fuvolix"]]["ff"],
+                                  "prefill_2048_tokens_ms": round(prefill_ms, 3), "prefill_tokens_per_s": round(2048 / prefill_ms * 1e3),
+                                  "decode_batch": args.batch, "decode_ms_per_step": round(decode_ms, 3),
+                                  "decode_tokens_per_s": round(args.batch / decode_ms * 1e3), "launches_per_decode_step": launches,
+                                  "weight_bytes": engine.model.weight_bytes, "step_kinds": engine.step_kinds}), flush=True)
+                del engine
+                torch.cuda.empty_cache()
+        for line in lipulorn_kernels(torch, size, peak):
+            print(json.dumps(dict(line, design="lipulorn", size=name)), flush=True)
+        for line in mixer_kernels(torch, FUVOLIX_SIZES[size["fuvolix"]], peak):
+            if line["kernel"].startswith("latent attention"):
+                print(json.dumps(dict(line, design="fuvolix", size=name)), flush=True)
+        for line in sumozen_kernels(torch, SUMOZEN_SIZES[size["sumozen"]], peak):
+            if line["kernel"].startswith(("capped attention", "gated delta rule")):
+                print(json.dumps(dict(line, design="sumozen", size=name)), flush=True)
+    return 0
+
+
 def run_compare(args):
     """Fuvolix beside GPT-2 of equal width, depth and inner size: the prompt step of 2,048 tokens
     (2 x 1,024) and the decode step of ``--batch`` requests at a context of 1,024, in bfloat16,
@@ -1141,6 +1356,8 @@ def main():
         return run_kernels()
     if args.compare == "sumozen":
         return run_compare_sumozen(args)
+    if args.compare == "lipulorn":
+        return run_compare_lipulorn(args)
     if args.compare:
         return run_compare(args)
     return run_ours(args)

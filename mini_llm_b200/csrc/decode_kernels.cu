@@ -229,8 +229,9 @@ split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
                        const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
                        const int* __restrict__ token_item, int n_heads, int n_kv_heads, int page_size, float scale,
-                       float cap, int window, int chunk, int max_chunks, float* __restrict__ part_acc,
-                       float* __restrict__ part_ml, int* __restrict__ counters) {
+                       float cap, int window, int block, const float* __restrict__ gate, long ld_gate, int chunk,
+                       int max_chunks, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                       int* __restrict__ counters) {
     constexpr int LPK = D / 8;             // lanes per key: each lane owns 8 of the head's dimensions
     constexpr int KPW = 32 / LPK;          // keys per warp per step
     dependents_may_start();
@@ -239,7 +240,9 @@ split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane % LPK, group = lane / LPK;
     const int p = positions[t];
-    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    // the first key seen: the window's, and with a mask of blocks of positions the first of the query's block
+    int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    if (block > 0) lo = max(lo, p - p % block);
     const int c_first = lo / chunk, c_last = p / chunk;
     if (c < c_first || c > c_last) return;
     const int begin = max(lo, c * chunk), end = min(p, c * chunk + chunk - 1);     // inclusive
@@ -375,21 +378,26 @@ split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
     float denom = 0.0f;
     for (int cc = c_first; cc <= c_last; cc++)
         denom += __ldcg(part_ml + (first + cc) * 2 + 1) * exp2f(__ldcg(part_ml + (first + cc) * 2) - top);
+    // a gate per (token, head) opens the result by its sigmoid
+    const float open = gate != nullptr ? 1.0f / (1.0f + __expf(-gate[(long)t * ld_gate + h])) : 1.0f;
     for (int d = threadIdx.x; d < D; d += 128) {
         float o = 0.0f;
         for (int cc = c_first; cc <= c_last; cc++)
             o += __ldcg(part_acc + (first + cc) * D + d) * exp2f(__ldcg(part_ml + (first + cc) * 2) - top);
-        out[(long)t * ld_out + (long)h * D + d] = __float2bfloat16_rn(o / denom);
+        out[(long)t * ld_out + (long)h * D + d] = __float2bfloat16_rn(o / denom * open);
     }
 }
 
-// (with a cap on the scores: score <- cap * tanh(score / cap); cap <= 0: none)
-extern "C" int mllm_decode_split_attention_capped(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,
+// (with a cap on the scores: score <- cap * tanh(score / cap); cap <= 0: none; with a mask of blocks of
+// positions: block > 0, a query sees only keys of its own block, counted from position 0; with a gate:
+// fp32 [tokens, >= heads], head h's result times sigmoid(gate[t, h]))
+extern "C" int mllm_decode_split_attention_masked(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,
                                                   const void* v_pages, const int* block_table, int max_blocks,
                                                   const int* positions, const int* token_item, int n_tokens, int n_heads,
                                                   int n_kv_heads, int head_size, int page_size, float scale, float cap,
-                                                  int window, int chunk, int max_chunks, float* part_acc, float* part_ml,
-                                                  int* counters, void* stream) {
+                                                  int window, int block, const float* gate, long ld_gate, int chunk,
+                                                  int max_chunks, float* part_acc, float* part_ml, int* counters,
+                                                  void* stream) {
     if (n_tokens <= 0) return 0;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
         return fail("split_attention: heads must be a multiple of key/value heads");
@@ -401,8 +409,8 @@ extern "C" int mllm_decode_split_attention_capped(void* out, long ld_out, const 
 #define LAUNCH_SPLIT(D)                                                                                              \
     launch_kernel(g_dependent_launch != 0, split_attention_kernel<D>, grid, dim3(128), 0, s, (bf16*)out, ld_out,     \
                   (const bf16*)q, ld_q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_blocks,         \
-                  positions, token_item, n_heads, n_kv_heads, page_size, scale, cap, window, chunk, max_chunks,      \
-                  part_acc, part_ml, counters)
+                  positions, token_item, n_heads, n_kv_heads, page_size, scale, cap, window, block, gate, ld_gate,   \
+                  chunk, max_chunks, part_acc, part_ml, counters)
     switch (head_size) {
     case 16: LAUNCH_SPLIT(16); break;
     case 32: LAUNCH_SPLIT(32); break;
@@ -413,6 +421,17 @@ extern "C" int mllm_decode_split_attention_capped(void* out, long ld_out, const 
     }
 #undef LAUNCH_SPLIT
     return check_launch("split_attention_kernel");
+}
+
+extern "C" int mllm_decode_split_attention_capped(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,
+                                                  const void* v_pages, const int* block_table, int max_blocks,
+                                                  const int* positions, const int* token_item, int n_tokens, int n_heads,
+                                                  int n_kv_heads, int head_size, int page_size, float scale, float cap,
+                                                  int window, int chunk, int max_chunks, float* part_acc, float* part_ml,
+                                                  int* counters, void* stream) {
+    return mllm_decode_split_attention_masked(out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions,
+                                              token_item, n_tokens, n_heads, n_kv_heads, head_size, page_size, scale, cap,
+                                              window, 0, nullptr, 0, chunk, max_chunks, part_acc, part_ml, counters, stream);
 }
 
 extern "C" int mllm_decode_split_attention(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,

@@ -132,18 +132,18 @@ class Kernels:
         read); steps of single tokens, and sizes the tiles do not take, one block per (token, head)."""
         self.launches += 1
         n = q.shape[0]
-        if (not self.plain_only and ctx.decode_only and n <= SPLIT_ATTENTION_MAX_ROWS and dim == vdim and not chunk and gate is None
+        if (not self.plain_only and ctx.decode_only and n <= SPLIT_ATTENTION_MAX_ROWS and dim == vdim
                 and dim in ops.SPLIT_ATTENTION_HEAD_SIZES and q.dtype == torch.bfloat16 and q.stride(0) % 8 == 0):
             # single tokens: each token's keys in chunks over many CTAs, merged by the last to arrive
             # (its exponentials, weights and sums are 32-bit, which this attention asks for)
             pairs = n * n_heads
-            chunk = 64 if pairs < 64 else (128 if pairs < 128 else (256 if pairs < 256 else 512))
+            span = 64 if pairs < 64 else (128 if pairs < 128 else (256 if pairs < 256 else 512))
             reach = cache.block_table.shape[1] * cache.page_size
             acc, ml, counters = self._scratch(ctx, SPLIT_ATTENTION_MAX_ROWS * n_heads, -(-reach // 64), dim)
             self.chose("capped_attention", "split_attention", n, n_heads, dim, vdim)
             return ops.split_attention(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.token_item,
-                                       n_heads, n_kv_heads, dim, cache.page_size, scale, window, chunk, -(-reach // chunk), acc,
-                                       ml, counters, cap=cap)
+                                       n_heads, n_kv_heads, dim, cache.page_size, scale, window, span, -(-reach // span), acc,
+                                       ml, counters, cap=cap, block=chunk, gate=gate)
         tiled = not ctx.decode_only and ops.capped_attention_tiled_takes(dim, vdim, q.dtype)
         self.chose("capped_attention", "capped_attention_tiled" if tiled else "capped_attention_plain", q.shape[0], n_heads, dim, vdim)
         return ops.capped_attention(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.token_item,

@@ -228,8 +228,8 @@ class _SkinnyParams(ctypes.Structure):
 
 
 _skinny = Function("decode", "mllm_decode_skinny_linear", [ctypes.POINTER(_SkinnyParams), P])
-_split_attention = Function("decode", "mllm_decode_split_attention_capped",
-                            [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, F, F, I, I, I, P, P, P, P])
+_split_attention = Function("decode", "mllm_decode_split_attention_masked",
+                            [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, F, F, I, I, P, L, I, I, P, P, P, P])
 
 SKINNY_MAX_SMEM = 200 * 1024
 SPLIT_ATTENTION_HEAD_SIZES = (16, 32, 64, 128, 256)
@@ -303,11 +303,13 @@ def skinny_linear(out, x, w, bias=None, epilogue="store", norm=None, scatter=Non
 
 
 def split_attention(out, q, k_pages, v_pages, block_table, positions, token_item, n_heads, n_kv_heads, head_size,
-                    page_size, scale, window, chunk, max_chunks, part_acc, part_ml, counters, cap=0.0):
+                    page_size, scale, window, chunk, max_chunks, part_acc, part_ml, counters, cap=0.0, block=0, gate=None):
     """Causal attention over the paged cache for few tokens: one CTA per (token, head, chunk
     of ``chunk`` keys); needs fp32 scratch ``part_acc`` [T*H*max_chunks*D], ``part_ml``
     [T*H*max_chunks*2] and zeroed int32 ``counters`` [T*H] (left zero).  ``cap`` > 0: the scores
-    are capped, cap * tanh(score / cap).  Scores, weights and sums are 32-bit."""
+    are capped, cap * tanh(score / cap).  ``block`` > 0: a query sees only the keys of its own block of
+    ``block`` positions (blocks counted from position 0).  ``gate`` fp32 [T, >= heads]: head h's result
+    is multiplied by sigmoid(gate[t, h]).  Scores, weights and sums are 32-bit."""
     _check(out, "split_attention.out", torch.bfloat16, 2)
     _check(q, "split_attention.q", torch.bfloat16, 2)
     _check(k_pages, "split_attention.k_pages", torch.bfloat16)
@@ -326,10 +328,15 @@ def split_attention(out, q, k_pages, v_pages, block_table, positions, token_item
         raise KernelError("split_attention: scratch too small")
     if max_chunks * chunk < page_size * block_table.shape[1]:
         raise KernelError("split_attention: the chunks do not cover the longest block table")
+    if gate is not None:
+        _check(gate, "split_attention.gate", torch.float32, 2)
+        if gate.shape[0] < n or gate.shape[1] < n_heads or gate.stride(1) != 1:
+            raise KernelError("split_attention: one gate per token and head")
     _split_attention(out.data_ptr(), out.stride(0), q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
                      block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), token_item.data_ptr(), n,
-                     n_heads, n_kv_heads, head_size, page_size, float(scale), float(cap or 0.0), int(window or 0), int(chunk),
-                     int(max_chunks), part_acc.data_ptr(), part_ml.data_ptr(), counters.data_ptr(), _stream())
+                     n_heads, n_kv_heads, head_size, page_size, float(scale), float(cap or 0.0), int(window or 0), int(block or 0),
+                     _ptr(gate), gate.stride(0) if gate is not None else 0, int(chunk), int(max_chunks), part_acc.data_ptr(),
+                     part_ml.data_ptr(), counters.data_ptr(), _stream())
     return out
 
 

@@ -24,7 +24,7 @@ class WeightSpec:
                bias: kept in 32-bit), "int_table" (kept as int32)
     transpose  the file stores [in, out]; the device copy is [out, in]
     init       how random-weights mode fills it: "matrix", "residual_matrix",
-               "table", "bias", "gain", "shift"
+               "table", "bias", "gain", "shift", "identity" (a square matrix that starts as the identity)
     optional   may be absent from the file (``fallback`` names the tensor used instead)
     keep_32bit a float tensor stored in 32-bit stays 32-bit in every mode
     """

@@ -34,7 +34,7 @@ class StreamConnection(Part):
         n, s = self.names, self.n_streams
         return [WeightSpec(self.full_name(n["read"]), (s,), role="vector", init="gain"),
                 WeightSpec(self.full_name(n["write"]), (s,), role="vector", init="gain"),
-                WeightSpec(self.full_name(n["mix"]), (s, s), role="vector", init="gain")]
+                WeightSpec(self.full_name(n["mix"]), (s, s), role="vector", init="identity")]
 
     def _streams(self, ctx):
         streams = getattr(ctx, "streams", None)

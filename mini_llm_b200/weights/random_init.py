@@ -69,13 +69,15 @@ def random_tensors(spec, seed: int, recipe: str = "gpt2") -> dict:
                 values = rng.normal(0.0, 0.02 / math.sqrt(2.0 * n_layers), size=shape)
             elif w.init == "gain":
                 values = np.ones(shape)
+            elif w.init == "identity":
+                values = np.eye(*shape)
             else:
                 values = np.zeros(shape)
             tensors[name] = values.astype(np.float32)
         else:
             if w.init in ("matrix", "table", "residual_matrix"):
                 values = rng.normal(0.0, 0.05, size=shape)
-            elif w.init == "gain":
+            elif w.init in ("gain", "identity"):
                 values = rng.uniform(0.5, 1.5, size=shape)
             elif w.init == "shift":
                 values = rng.normal(0.0, 0.1, size=shape)
