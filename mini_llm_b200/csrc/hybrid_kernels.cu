@@ -645,6 +645,16 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
     T raw[PER], raw_v[VPER];
     float raw_a = 0.0f, raw_b = 0.0f;
     float raw_g[GPER];
+    // (the channel's bias is the same in every chunk: it is read once here, and added when the chunk is staged,
+    // so that asking for a chunk waits for nothing)
+    float bias_g[GPER];
+    if (CHANNEL) {
+#pragma unroll
+        for (int i = 0; i < GPER; i++) {
+            const int d = (threadIdx.x + 128 * i) % (DPT * LANES);
+            bias_g[i] = d < dim ? pp.step_bias[(long)head * dim + d] : 0.0f;
+        }
+    }
     auto ask = [&](int start) {
         const int n = min(TOK, count - start);
         const long t0 = first + start;
@@ -666,8 +676,7 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
 #pragma unroll
             for (int i = 0; i < GPER; i++) {
                 const int u = threadIdx.x + 128 * i, tt = u / (DPT * LANES), d = u % (DPT * LANES);
-                raw_g[i] = (tt < n && d < dim) ? pp.gate_a[(t0 + tt) * pp.ld_gate_a + (long)head * dim + d] + pp.step_bias[(long)head * dim + d]
-                                               : 0.0f;
+                raw_g[i] = (tt < n && d < dim) ? pp.gate_a[(t0 + tt) * pp.ld_gate_a + (long)head * dim + d] : 0.0f;
             }
         }
     };
@@ -695,7 +704,7 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
 #pragma unroll
             for (int i = 0; i < GPER; i++) {
                 const int u = threadIdx.x + 128 * i, tt = u / (DPT * LANES), d = u % (DPT * LANES);
-                if (tt < TOK) gs[tt * ROW + (d / DPT) * PAD + d % DPT] = expf(-rate * softplus_f(raw_g[i]));
+                if (tt < TOK) gs[tt * ROW + (d / DPT) * PAD + d % DPT] = expf(-rate * softplus_f(raw_g[i] + bias_g[i]));
             }
         }
         __syncthreads();
@@ -775,7 +784,8 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
                     sum_k[c] += __shfl_xor_sync(0xffffffffu, sum_k[c], o);
                     sum_q[c] += __shfl_xor_sync(0xffffffffu, sum_q[c], o);
                 }
-            const float a = as[tt], b = bs[tt], both = kq[tt];
+            // (with a decay per key channel the rows have decayed already: a factor of one, known when compiled)
+            const float a = CHANNEL ? 1.0f : as[tt], b = bs[tt], both = kq[tt];
 #pragma unroll
             for (int c = 0; c < CPT; c++) {
                 const float value = vs[tt * COLS + col_local + c * GROUPS];

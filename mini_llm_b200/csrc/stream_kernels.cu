@@ -35,7 +35,9 @@ extern "C" int mllm_streams_fill(float* streams, const float* hidden, int n_stre
     return check_launch("streams_fill_kernel");
 }
 
-template <typename T>
+// VEC: 4 (every row starts on a 16-byte boundary and the width is a multiple of four: four columns a thread,
+// moved as one vector) or 1
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 streams_step_kernel(float* __restrict__ streams, const float* __restrict__ y, long ld_y, const float* __restrict__ mix,
                     const float* __restrict__ w_out, int read, const float* __restrict__ w_in, float* __restrict__ u_out,
@@ -55,39 +57,75 @@ streams_step_kernel(float* __restrict__ streams, const float* __restrict__ y, lo
     __syncthreads();
     float* mine = streams + (long)t * n_streams * width;
     float sq = 0.0f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float x[MAX_STREAMS];
+    for (int c = threadIdx.x * VEC; c < width; c += blockDim.x * VEC) {
+        float x[MAX_STREAMS][VEC];
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; s++) x[s] = s < n_streams ? mine[(long)s * width + c] : 0.0f;
+        for (int s = 0; s < MAX_STREAMS; s++) {
+            if (s < n_streams) {
+                if (VEC == 4) {
+                    const float4 v = *reinterpret_cast<const float4*>(mine + (long)s * width + c);
+                    x[s][0] = v.x, x[s][VEC > 1 ? 1 : 0] = v.y, x[s][VEC > 1 ? 2 : 0] = v.z, x[s][VEC > 1 ? 3 : 0] = v.w;
+                } else {
+                    x[s][0] = mine[(long)s * width + c];
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) x[s][e] = 0.0f;
+            }
+        }
         if (y != nullptr) {
-            const float result = y[(long)t * ld_y + c];
-            float fresh[MAX_STREAMS];
+            float result[VEC];
+            if (VEC == 4) {
+                const float4 v = *reinterpret_cast<const float4*>(y + (long)t * ld_y + c);
+                result[0] = v.x, result[VEC > 1 ? 1 : 0] = v.y, result[VEC > 1 ? 2 : 0] = v.z, result[VEC > 1 ? 3 : 0] = v.w;
+            } else {
+                result[0] = y[(long)t * ld_y + c];
+            }
+            float fresh[MAX_STREAMS][VEC];
 #pragma unroll
             for (int to = 0; to < MAX_STREAMS; to++) {
                 if (to >= n_streams) continue;
-                float sum = 0.0f;
 #pragma unroll
-                for (int s = 0; s < MAX_STREAMS; s++)
-                    if (s < n_streams) sum = fmaf(m[s * n_streams + to], x[s], sum);
-                fresh[to] = fmaf(o[to], result, sum);
+                for (int e = 0; e < VEC; e++) {
+                    float sum = 0.0f;
+#pragma unroll
+                    for (int s = 0; s < MAX_STREAMS; s++)
+                        if (s < n_streams) sum = fmaf(m[s * n_streams + to], x[s][e], sum);
+                    fresh[to][e] = fmaf(o[to], result[e], sum);
+                }
             }
 #pragma unroll
-            for (int s = 0; s < MAX_STREAMS; s++)
-                if (s < n_streams) mine[(long)s * width + c] = x[s] = fresh[s];
+            for (int s = 0; s < MAX_STREAMS; s++) {
+                if (s >= n_streams) continue;
+#pragma unroll
+                for (int e = 0; e < VEC; e++) x[s][e] = fresh[s][e];
+                if (VEC == 4)
+                    *reinterpret_cast<float4*>(mine + (long)s * width + c) =
+                        make_float4(x[s][0], x[s][VEC > 1 ? 1 : 0], x[s][VEC > 1 ? 2 : 0], x[s][VEC > 1 ? 3 : 0]);
+                else
+                    mine[(long)s * width + c] = x[s][0];
+            }
         }
         if (read) {
-            float u = 0.0f;
 #pragma unroll
-            for (int s = 0; s < MAX_STREAMS; s++)
-                if (s < n_streams) u = fmaf(in[s], x[s], u);
-            if (u_out != nullptr) u_out[(long)t * ld_u + c] = u;
-            u_row[c] = u;
-            sq = fmaf(u, u, sq);
+            for (int e = 0; e < VEC; e++) {
+                float u = 0.0f;
+#pragma unroll
+                for (int s = 0; s < MAX_STREAMS; s++)
+                    if (s < n_streams) u = fmaf(in[s], x[s][e], u);
+                if (u_out != nullptr) u_out[(long)t * ld_u + c + e] = u;
+                u_row[c + e] = u;
+                sq = fmaf(u, u, sq);
+            }
         }
     }
     if (!read || normed == nullptr) return;
+    // (every thread reads back the columns it wrote itself: no barrier is needed before the sum's own)
     const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
-    for (int c = threadIdx.x; c < width; c += blockDim.x) normed[(long)t * ld_normed + c] = from_f32<T>(u_row[c] * inv * gain[c]);
+    for (int c = threadIdx.x * VEC; c < width; c += blockDim.x * VEC) {
+#pragma unroll
+        for (int e = 0; e < VEC; e++) normed[(long)t * ld_normed + c + e] = from_f32<T>(u_row[c + e] * inv * gain[c + e]);
+    }
 }
 
 extern "C" int mllm_streams_step(float* streams, const float* y, long ld_y, const float* mix, const float* w_out, int read,
@@ -101,32 +139,47 @@ extern "C" int mllm_streams_step(float* streams, const float* y, long ld_y, cons
     const size_t shared = (size_t)width * sizeof(float);
     if (shared > 200 * 1024) return fail("streams_step: the row does not fit in shared memory");
     cudaStream_t s = (cudaStream_t)stream;
+    const bool vec = width % 4 == 0 && ((uintptr_t)streams & 15) == 0 &&
+                     (y == nullptr || (((uintptr_t)y & 15) == 0 && ld_y % 4 == 0));
+#define LAUNCH_STREAMS(T, VEC)                                                                                                \
+    do {                                                                                                                      \
+        if (shared > 48 * 1024)                                                                                               \
+            cudaFuncSetAttribute(streams_step_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);      \
+        launch_kernel(g_dependent_launch != 0, streams_step_kernel<T, VEC>, dim3(n_tokens), dim3(256), shared, s, streams, y, \
+                      ld_y, mix, w_out, read, w_in, u_out, ld_u, (T*)normed, ld_normed, gain, eps, n_streams, width);         \
+    } while (0)
     if (dtype == DT_F32) {
-        if (shared > 48 * 1024) cudaFuncSetAttribute(streams_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-        launch_kernel(g_dependent_launch != 0, streams_step_kernel<float>, dim3(n_tokens), dim3(256), shared, s, streams, y, ld_y, mix,
-                      w_out, read, w_in, u_out, ld_u, (float*)normed, ld_normed, gain, eps, n_streams, width);
+        if (vec) LAUNCH_STREAMS(float, 4); else LAUNCH_STREAMS(float, 1);
     } else if (dtype == DT_BF16) {
-        if (shared > 48 * 1024) cudaFuncSetAttribute(streams_step_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-        launch_kernel(g_dependent_launch != 0, streams_step_kernel<bf16>, dim3(n_tokens), dim3(256), shared, s, streams, y, ld_y, mix,
-                      w_out, read, w_in, u_out, ld_u, (bf16*)normed, ld_normed, gain, eps, n_streams, width);
+        if (vec) LAUNCH_STREAMS(bf16, 4); else LAUNCH_STREAMS(bf16, 1);
     } else {
         return fail("streams_step: unknown dtype");
     }
+#undef LAUNCH_STREAMS
     return check_launch("streams_step_kernel");
 }
 
-// out[t, f] = act(gu[t, f]) * gu[t, inner + f]; act: 0 silu, 1 gelu (tanh form), 2 none
-template <typename T>
+// out[t, f] = act(gu[t, f]) * gu[t, inner + f]; act: 0 silu, 1 gelu (tanh form), 2 none.  VEC entries a thread:
+// 16 bytes where every row and both halves start on such a boundary, else one.
+template <typename T, int VEC>
 __global__ void gated_act_kernel(T* __restrict__ out, long ld_out, const T* __restrict__ gu, long ld_gu, int inner, int act,
                                  long n) {
     dependents_may_start();
     wait_for_earlier_kernels();
-    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (i >= n) return;
     const long t = i / inner, f = i % inner;
-    const float gate = to_f32(gu[t * ld_gu + f]), up = to_f32(gu[t * ld_gu + inner + f]);
-    const float a = act == 0 ? gate / (1.0f + expf(-gate)) : (act == 1 ? gelu_tanh_f(gate) : gate);
-    out[t * ld_out + f] = from_f32<T>(a * up);
+    struct alignas(sizeof(T) * VEC) Pack { T e[VEC]; };
+    const Pack gate = *reinterpret_cast<const Pack*>(gu + t * ld_gu + f);
+    const Pack up = *reinterpret_cast<const Pack*>(gu + t * ld_gu + inner + f);
+    Pack result;
+#pragma unroll
+    for (int e = 0; e < VEC; e++) {
+        const float g = to_f32(gate.e[e]);
+        const float a = act == 0 ? g / (1.0f + expf(-g)) : (act == 1 ? gelu_tanh_f(g) : g);
+        result.e[e] = from_f32<T>(a * to_f32(up.e[e]));
+    }
+    *reinterpret_cast<Pack*>(out + t * ld_out + f) = result;
 }
 
 extern "C" int mllm_streams_gated_act(void* out, long ld_out, const void* gu, long ld_gu, int inner, int act, int n_tokens,
@@ -135,13 +188,18 @@ extern "C" int mllm_streams_gated_act(void* out, long ld_out, const void* gu, lo
     if (inner <= 0 || act < 0 || act > 2) return fail("gated_act: bad sizes or activation");
     const long n = (long)n_tokens * inner;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == DT_F32)
-        launch_kernel(g_dependent_launch != 0, gated_act_kernel<float>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, (float*)out,
-                      ld_out, (const float*)gu, ld_gu, inner, act, n);
-    else if (dtype == DT_BF16)
-        launch_kernel(g_dependent_launch != 0, gated_act_kernel<bf16>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, (bf16*)out,
-                      ld_out, (const bf16*)gu, ld_gu, inner, act, n);
-    else
+    const int size = dtype == DT_F32 ? 4 : 2, wide = 16 / size;
+    const bool vec = inner % wide == 0 && ld_gu % wide == 0 && ld_out % wide == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0;
+#define LAUNCH_GATED(T, VEC)                                                                                                   \
+    launch_kernel(g_dependent_launch != 0, gated_act_kernel<T, VEC>, dim3((unsigned)((n / VEC + 255) / 256)), dim3(256), 0, s, \
+                  (T*)out, ld_out, (const T*)gu, ld_gu, inner, act, n)
+    if (dtype == DT_F32) {
+        if (vec) LAUNCH_GATED(float, 4); else LAUNCH_GATED(float, 1);
+    } else if (dtype == DT_BF16) {
+        if (vec) LAUNCH_GATED(bf16, 8); else LAUNCH_GATED(bf16, 1);
+    } else {
         return fail("gated_act: unknown dtype");
+    }
+#undef LAUNCH_GATED
     return check_launch("gated_act_kernel");
 }
