@@ -208,16 +208,21 @@ class CacheManager:
             self.on_free(group.index, pages)
 
     def commit(self, slot: int, n_new: int) -> None:
-        """``n_new`` tokens were stored.  Pages a window has passed are given back."""
+        """``n_new`` tokens were stored.  Pages a window (or a block of positions) has passed are given back."""
         request = self._take(slot)
         if request.length + n_new > request.reserved:
             raise PageError(f"slot {slot}: committing {n_new} tokens beyond what was reserved")
         request.length += n_new
         for group in self.groups:
-            if not group.paged or group.need.window is None:
+            if not group.paged or (group.need.window is None and group.need.block is None):
                 continue
-            # The next query sits at position >= length and sees keys > length - window.
-            first_needed = max(0, request.length - group.need.window + 1)
+            # The next query sits at position >= length: it sees keys > length - window, and with a mask of
+            # blocks of positions none before the first position of the block that position `length` lies in.
+            first_needed = 0
+            if group.need.window is not None:
+                first_needed = max(0, request.length - group.need.window + 1)
+            if group.need.block is not None:
+                first_needed = max(first_needed, request.length // group.need.block * group.need.block)
             keep_from = min(first_needed // self.page_size, request.n_blocks[group.index])
             first = request.first_block[group.index]
             if keep_from > first:

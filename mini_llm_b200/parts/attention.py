@@ -239,7 +239,7 @@ class GatedAttention(Mixer):
         return specs
 
     def cache_need(self):
-        return PagedKV(self.n_kv_heads, self.dim, self.window, value_size=self.vdim)
+        return PagedKV(self.n_kv_heads, self.dim, self.window, value_size=self.vdim, block=self.chunk)
 
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)

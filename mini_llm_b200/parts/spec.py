@@ -110,8 +110,9 @@ class ModelSpec:
 
 @dataclass(frozen=True)
 class PagedKV:
-    """Keys and values of every cached token (or of the last ``window`` tokens), in pages.
-    With ``has_values`` false only one row per token is kept (the ``keys``): a mixer whose values
+    """Keys and values of every cached token (or of the last ``window`` tokens; or, with ``block``, of
+    the tokens of the newest block of that many positions, where queries read keys of their own block
+    only), in pages.  With ``has_values`` false only one row per token is kept (the ``keys``): a mixer whose values
     are a part of that row (attention over a shared latent) needs no second pool.  ``value_size``:
     the size of a value per head where it differs from the keys' ``head_size``."""
 
@@ -120,6 +121,7 @@ class PagedKV:
     window: int | None = None          # None: all keys
     has_values: bool = True
     value_size: int | None = None      # None: as head_size
+    block: int | None = None           # None: no blocks; else keys before the newest block of positions are never read again
 
 
 @dataclass(frozen=True)

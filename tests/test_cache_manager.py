@@ -81,6 +81,29 @@ def test_request_cannot_outgrow_its_positions():
     assert not m.reserve(s, 1) and not m.can_reserve(s, 1)
 
 
+def test_block_group_keeps_the_newest_block_of_positions():
+    """Queries that read keys of their own block of 24 positions only: once a request is past a block, the
+    block's pages go back (the page in which the newest block starts stays)."""
+    blocks = PagedKV(2, 16, block=24)
+    both = PagedKV(2, 16, window=20, block=24)
+    m = CacheManager([FULL, blocks, both], page_size=8, n_pages=[32, 9, 9], max_requests=2, max_tokens_per_request=200)
+    s = m.open()
+    length = 0
+    for n in [5, 30, 1, 1, 11, 2, 40, 1, 5]:
+        assert m.reserve(s, n), (length, n)
+        m.commit(s, n)
+        length += n
+        m.check()
+        for group, first_key in ((1, length // 24 * 24), (2, max(length // 24 * 24, length - 20 + 1, 0))):
+            first_needed = first_key // 8
+            row = m.block_table_row(group, s)
+            assert (row[:first_needed] == NO_PAGE).all() and (row[first_needed:-(-length // 8)] != NO_PAGE).all()
+            assert m.pages_held(s)[group] == -(-length // 8) - first_needed <= 4
+    m.close(s)
+    assert m.pages_free() == [32, 9, 9]
+    m.check()
+
+
 def test_window_group_gives_pages_back_as_it_passes_them():
     m = CacheManager([FULL, WINDOW], page_size=8, n_pages=[32, 9], max_requests=2, max_tokens_per_request=200)
     s = m.open()

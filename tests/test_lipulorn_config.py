@@ -70,7 +70,7 @@ def test_what_the_layers_keep():
     needs = model.cache_needs()
     # the latent rows stay as long as the widest window of the layers that read them (11, 17 and 4)
     assert needs[0] == PagedKV(1, 40 + 8, 17, has_values=False)
-    assert needs[1] == PagedKV(2, 12, None, value_size=20)
+    assert needs[1] == PagedKV(2, 12, None, value_size=20, block=9)       # keys before the newest block are never read again
     assert needs[2] == {"mixer.state": FixedState((4 * 12 * 20,), "float32"), "mixer.taps": FixedState((2, 2 * 2 * 12 + 4 * 20), "float32")}
     assert needs[3] is None and needs[6] is None           # they read layer 0's rows
     assert needs[4] == {"mixer.state": FixedState((2 * 20 * 8,), "float32"), "mixer.taps": FixedState((1, 2 * 2 * 20 + 2 * 8), "float32")}

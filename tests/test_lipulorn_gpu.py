@@ -203,10 +203,11 @@ def test_attention_block_edges_and_a_far_key(tmp_path, chunk):
     from position 0 whatever the cut."""
     raw, bend = _marked_attention("attention", chunk=chunk)
     folder = lp.make_model(str(tmp_path / "m"), raw, seed=14, bend=bend, matrix_scale=2.0)
-    engine = engine_for(folder)
+    engine = engine_for(folder, debug_poison=True)
     length = 300
     inside = (length - 1) % chunk                  # the distance from the last position to its block's first
     _edge_cases(engine, folder, length, (None, 0 if inside == 0 else 1, inside, inside + 1), [(inside, inside + 1)])
+    assert engine.cache.freed_by_window > 0        # the pages of the blocks a request has left went back (and were poisoned)
 
 
 def test_shared_rows_through_a_wider_and_a_narrower_window(tmp_path):
