@@ -192,6 +192,7 @@ class StepContext:
         self.item_slot = self.item_offset = self.item_count = self.item_start = None    # the same, on the device (int32)
         self.kept_results = None      # fp32 [T, planes, width]: the embedding output and every layer's result, if the model keeps them
         self.streams = None           # fp32 [T, streams, width]: the residual of a model with several residual streams
+        self.streams_pending = None   # a layer's last write onto the streams, waiting to go with the next read-out
         self.decode_only = False      # every entry brings exactly one token
         self.fused = False            # the step goes to the one-kernel decode step
         self.dump = None              # a list: the model appends the residual stream after every run entry

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 from ..parts.base import build_part, get_arrangement
 from ..parts.spec import NoCache
+from ..parts.streams import read_sum
 from ..weights.loader import collect_specs, load_weights
 
 
@@ -100,7 +101,7 @@ class Model:
             ctx.kept_results = ctx.buffer("kept_results", (ctx.n_tokens, len(self.spec.order) + 1, self.spec.hidden_size),
                                           hidden.dtype)
             ctx.kernels.depth_mix(hidden, ctx.kept_results, None, 0)
-        ctx.streams = None
+        ctx.streams = ctx.streams_pending = None
         if self.spec.residual_streams > 0:
             # several residual streams, all equal to the embedding output at the start
             ctx.streams = ctx.buffer("streams", (ctx.n_tokens, self.spec.residual_streams, self.spec.hidden_size), hidden.dtype)
@@ -113,12 +114,12 @@ class Model:
             arrangement.run(ctx, parts, hidden, cache_views[index])
             if dump is not None:
                 if ctx.streams is not None:
-                    ctx.kernels.streams_step(ctx.streams, read=True, u_out=hidden)      # the sum of the streams
+                    read_sum(ctx, hidden)
                 dump.append(hidden.clone())
         if ctx.n_want == 0:
             return None
         if ctx.streams is not None:
-            ctx.kernels.streams_step(ctx.streams, read=True, u_out=hidden)
+            read_sum(ctx, hidden)
         defer = getattr(self.final_norm, "can_defer", False) and getattr(self.head, "accepts_deferred_norm", False)
         rows = self.final_norm.forward(ctx, hidden, rows=ctx.want_rows, tag="final_norm",
                                        **({"defer": True} if defer else {}))

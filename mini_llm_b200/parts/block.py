@@ -77,13 +77,14 @@ class HyperConnections(Arrangement):
         if getattr(cache, "kind", "none") == "composite":
             cache = cache.sub("mixer")
         y = parts["mixer"].compute(ctx, x, cache)
+        # the layer's last write waits for the next read-out of the streams (the next layer's, or the model's sum)
         if "feed_forward" not in parts:
-            first.write(ctx, y)
+            first.write(ctx, y, defer=True)
             return
         # the mixer's result goes onto the streams and the feed-forward's input comes off them in one pass
         second = parts["streams_2"]
         x = first.write_then_read(ctx, y, second, parts["norm_2"], tag="norm_2")
-        second.write(ctx, parts["feed_forward"].compute(ctx, x))
+        second.write(ctx, parts["feed_forward"].compute(ctx, x), defer=True)
 
 
 register_arrangement("pre_norm", PreNorm())

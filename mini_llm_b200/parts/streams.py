@@ -9,7 +9,9 @@ weights and sums are 32-bit.
 ``stream_connection`` is the connection of one sublayer: its three weight tensors and the passes
 over ``ctx.streams`` [T, n_streams, width].  A pass is one kernel: the write of one sublayer's
 result, the read-out for the next sublayer and that sublayer's norm (an RMS norm over the whole
-width) may be one pass.
+width) may be one pass.  A layer's last write may wait (``write(defer=True)``) for the next read-out of
+the streams, the next layer's or the model's final sum, and go with it in one pass; the result that
+waits must stay untouched until then (``ctx.streams_pending``).
 """
 
 from __future__ import annotations
@@ -18,6 +20,25 @@ import torch
 
 from .base import Part, register_part
 from .spec import WeightSpec
+
+
+def take_pending(ctx) -> dict:
+    """The arguments of the write that waits for the next pass over the streams (none: an empty dict)."""
+    pending = getattr(ctx, "streams_pending", None) or {}
+    ctx.streams_pending = None
+    return pending
+
+
+def flush(ctx) -> None:
+    """The write that waits, as a pass of its own."""
+    pending = take_pending(ctx)
+    if pending:
+        ctx.kernels.streams_step(ctx.streams, **pending)
+
+
+def read_sum(ctx, out) -> None:
+    """The plain sum of the streams (the model's residual) into ``out`` (fp32 [T, width]), after the write that waits."""
+    ctx.kernels.streams_step(ctx.streams, read=True, u_out=out, **take_pending(ctx))
 
 
 class StreamConnection(Part):
@@ -65,11 +86,18 @@ class StreamConnection(Part):
         return dict(y=y, mix=self.w(self.names["mix"]), w_out=self.w(self.names["write"]))
 
     def read(self, ctx, norm, tag="norm_1"):
-        """The normed read-out of the streams: what this connection's sublayer takes in."""
-        return self._pass(ctx, norm, tag, self)
+        """The normed read-out of the streams: what this connection's sublayer takes in.  A write that
+        waits goes first, in the same pass."""
+        return self._pass(ctx, norm, tag, self, **take_pending(ctx))
 
-    def write(self, ctx, y):
-        """The sublayer's result ``y`` (fp32 [T, width]) onto the streams."""
+    def write(self, ctx, y, defer=False):
+        """The sublayer's result ``y`` (fp32 [T, width]) onto the streams; with ``defer`` together with the
+        next read-out of the streams, whoever asks for it."""
+        if defer:
+            flush(ctx)
+            self._streams(ctx)
+            ctx.streams_pending = self._write_arguments(y)
+            return
         ctx.kernels.streams_step(self._streams(ctx), **self._write_arguments(y))
 
     def write_then_read(self, ctx, y, reader, norm, tag="norm_2"):

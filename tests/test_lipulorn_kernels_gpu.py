@@ -184,7 +184,8 @@ def test_head_norms_and_cache_store():
 
 # ---- the delta rule with a decay per key channel -----------------------------------------------------------
 
-@pytest.mark.parametrize("heads, qk_heads, dim, vdim", [(2, 1, 8, 8), (3, 3, 20, 12), (4, 2, 64, 64), (1, 1, 128, 40), (60, 4, 12, 16)])
+@pytest.mark.parametrize("heads, qk_heads, dim, vdim", [(2, 1, 8, 8), (3, 3, 20, 12), (4, 2, 64, 64), (1, 1, 128, 40), (60, 4, 12, 16),
+                                                        (2, 1, 256, 24), (1, 1, 520, 8)])
 def test_channel_decay_recurrence_carries_its_state(heads, qk_heads, dim, vdim):
     """A sequence cut in six (down to one token) against the token-by-token formulas; the decay multiplies
     the rows of the state before the old state is read."""
