@@ -36,13 +36,16 @@ extern "C" int mllm_streams_fill(float* streams, const float* hidden, int n_stre
 }
 
 // VEC: 4 (every row starts on a 16-byte boundary and the width is a multiple of four: four columns a thread,
-// moved as one vector) or 1
-template <typename T, int VEC>
+// moved as one vector) or 1.  NS: the number of streams where it is known when compiled (1 to 4: the sums
+// unroll to what is needed and the kernel's registers allow more blocks an SM), or 0 for any number up to 8.
+template <typename T, int VEC, int NS>
 __global__ void __launch_bounds__(256)
 streams_step_kernel(float* __restrict__ streams, const float* __restrict__ y, long ld_y, const float* __restrict__ mix,
                     const float* __restrict__ w_out, int read, const float* __restrict__ w_in, float* __restrict__ u_out,
                     long ld_u, T* __restrict__ normed, long ld_normed, const float* __restrict__ gain, float eps, int n_streams,
                     int width) {
+    constexpr int BOUND = NS > 0 ? NS : MAX_STREAMS;
+    if (NS > 0) n_streams = NS;
     dependents_may_start();
     wait_for_earlier_kernels();
     extern __shared__ float u_row[];                 // [width]: the read-out, until it is normed
@@ -58,64 +61,62 @@ streams_step_kernel(float* __restrict__ streams, const float* __restrict__ y, lo
     float* mine = streams + (long)t * n_streams * width;
     float sq = 0.0f;
     for (int c = threadIdx.x * VEC; c < width; c += blockDim.x * VEC) {
-        float x[MAX_STREAMS][VEC];
+        alignas(16) float x[BOUND][VEC];
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; s++) {
+        for (int s = 0; s < BOUND; s++) {
             if (s < n_streams) {
-                if (VEC == 4) {
-                    const float4 v = *reinterpret_cast<const float4*>(mine + (long)s * width + c);
-                    x[s][0] = v.x, x[s][VEC > 1 ? 1 : 0] = v.y, x[s][VEC > 1 ? 2 : 0] = v.z, x[s][VEC > 1 ? 3 : 0] = v.w;
-                } else {
+                if constexpr (VEC == 4)
+                    *reinterpret_cast<float4*>(x[s]) = *reinterpret_cast<const float4*>(mine + (long)s * width + c);
+                else
                     x[s][0] = mine[(long)s * width + c];
-                }
             } else {
 #pragma unroll
                 for (int e = 0; e < VEC; e++) x[s][e] = 0.0f;
             }
         }
-        if (y != nullptr) {
-            float result[VEC];
-            if (VEC == 4) {
-                const float4 v = *reinterpret_cast<const float4*>(y + (long)t * ld_y + c);
-                result[0] = v.x, result[VEC > 1 ? 1 : 0] = v.y, result[VEC > 1 ? 2 : 0] = v.z, result[VEC > 1 ? 3 : 0] = v.w;
-            } else {
-                result[0] = y[(long)t * ld_y + c];
-            }
-            float fresh[MAX_STREAMS][VEC];
+        // the read-out of the streams as they then are; a new stream goes to memory as soon as it is summed (the old
+        // ones stay in registers until all are), and into the read-out
+        alignas(16) float u[VEC];
 #pragma unroll
-            for (int to = 0; to < MAX_STREAMS; to++) {
+        for (int e = 0; e < VEC; e++) u[e] = 0.0f;
+        if (y != nullptr) {
+            alignas(16) float result[VEC];
+            if constexpr (VEC == 4)
+                *reinterpret_cast<float4*>(result) = *reinterpret_cast<const float4*>(y + (long)t * ld_y + c);
+            else
+                result[0] = y[(long)t * ld_y + c];
+#pragma unroll
+            for (int to = 0; to < BOUND; to++) {
                 if (to >= n_streams) continue;
+                alignas(16) float fresh[VEC];
 #pragma unroll
                 for (int e = 0; e < VEC; e++) {
                     float sum = 0.0f;
 #pragma unroll
-                    for (int s = 0; s < MAX_STREAMS; s++)
+                    for (int s = 0; s < BOUND; s++)
                         if (s < n_streams) sum = fmaf(m[s * n_streams + to], x[s][e], sum);
-                    fresh[to][e] = fmaf(o[to], result[e], sum);
+                    fresh[e] = fmaf(o[to], result[e], sum);
+                    u[e] = fmaf(in[to], fresh[e], u[e]);
                 }
-            }
-#pragma unroll
-            for (int s = 0; s < MAX_STREAMS; s++) {
-                if (s >= n_streams) continue;
-#pragma unroll
-                for (int e = 0; e < VEC; e++) x[s][e] = fresh[s][e];
-                if (VEC == 4)
-                    *reinterpret_cast<float4*>(mine + (long)s * width + c) =
-                        make_float4(x[s][0], x[s][VEC > 1 ? 1 : 0], x[s][VEC > 1 ? 2 : 0], x[s][VEC > 1 ? 3 : 0]);
+                if constexpr (VEC == 4)
+                    *reinterpret_cast<float4*>(mine + (long)to * width + c) = *reinterpret_cast<const float4*>(fresh);
                 else
-                    mine[(long)s * width + c] = x[s][0];
+                    mine[(long)to * width + c] = fresh[0];
             }
+        } else {
+#pragma unroll
+            for (int s = 0; s < BOUND; s++)
+                if (s < n_streams) {
+#pragma unroll
+                    for (int e = 0; e < VEC; e++) u[e] = fmaf(in[s], x[s][e], u[e]);
+                }
         }
         if (read) {
 #pragma unroll
             for (int e = 0; e < VEC; e++) {
-                float u = 0.0f;
-#pragma unroll
-                for (int s = 0; s < MAX_STREAMS; s++)
-                    if (s < n_streams) u = fmaf(in[s], x[s][e], u);
-                if (u_out != nullptr) u_out[(long)t * ld_u + c + e] = u;
-                u_row[c + e] = u;
-                sq = fmaf(u, u, sq);
+                if (u_out != nullptr) u_out[(long)t * ld_u + c + e] = u[e];
+                u_row[c + e] = u[e];
+                sq = fmaf(u[e], u[e], sq);
             }
         }
     }
@@ -141,12 +142,22 @@ extern "C" int mllm_streams_step(float* streams, const float* y, long ld_y, cons
     cudaStream_t s = (cudaStream_t)stream;
     const bool vec = width % 4 == 0 && ((uintptr_t)streams & 15) == 0 &&
                      (y == nullptr || (((uintptr_t)y & 15) == 0 && ld_y % 4 == 0));
-#define LAUNCH_STREAMS(T, VEC)                                                                                                \
-    do {                                                                                                                      \
-        if (shared > 48 * 1024)                                                                                               \
-            cudaFuncSetAttribute(streams_step_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);      \
-        launch_kernel(g_dependent_launch != 0, streams_step_kernel<T, VEC>, dim3(n_tokens), dim3(256), shared, s, streams, y, \
-                      ld_y, mix, w_out, read, w_in, u_out, ld_u, (T*)normed, ld_normed, gain, eps, n_streams, width);         \
+#define LAUNCH_STREAMS_AS(T, VEC, NS)                                                                                            \
+    do {                                                                                                                         \
+        if (shared > 48 * 1024)                                                                                                  \
+            cudaFuncSetAttribute(streams_step_kernel<T, VEC, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);     \
+        launch_kernel(g_dependent_launch != 0, streams_step_kernel<T, VEC, NS>, dim3(n_tokens), dim3(256), shared, s, streams,   \
+                      y, ld_y, mix, w_out, read, w_in, u_out, ld_u, (T*)normed, ld_normed, gain, eps, n_streams, width);         \
+    } while (0)
+#define LAUNCH_STREAMS(T, VEC)                                                                                                   \
+    do {                                                                                                                         \
+        switch (n_streams) {                                                                                                     \
+        case 1: LAUNCH_STREAMS_AS(T, VEC, 1); break;                                                                             \
+        case 2: LAUNCH_STREAMS_AS(T, VEC, 2); break;                                                                             \
+        case 3: LAUNCH_STREAMS_AS(T, VEC, 3); break;                                                                             \
+        case 4: LAUNCH_STREAMS_AS(T, VEC, 4); break;                                                                             \
+        default: LAUNCH_STREAMS_AS(T, VEC, 0); break;                                                                            \
+        }                                                                                                                        \
     } while (0)
     if (dtype == DT_F32) {
         if (vec) LAUNCH_STREAMS(float, 4); else LAUNCH_STREAMS(float, 1);
@@ -155,6 +166,7 @@ extern "C" int mllm_streams_step(float* streams, const float* y, long ld_y, cons
     } else {
         return fail("streams_step: unknown dtype");
     }
+#undef LAUNCH_STREAMS_AS
 #undef LAUNCH_STREAMS
     return check_launch("streams_step_kernel");
 }
