@@ -779,7 +779,7 @@ def fuvolix_config(size: dict, vocab: int) -> dict:
             "canon": {"taps": 4}, "layers": [three[i % 3] for i in range(size["layers"])]}
 
 
-def mixer_kernels(torch, size: dict, peak: dict):
+def mixer_kernels(torch, size: dict, peak: dict, memories=("mlstm", "lightning")):
     """The mixers' kernels alone, replayed back to back on operands of their own: prompt portions
     (2 x 1,024 tokens) and single tokens (8 requests at 1,023 cached tokens), each with the work it
     must do and the fraction of its bound: 32-bit FMA (nominal) where the sums are 32-bit by the
@@ -859,7 +859,7 @@ def mixer_kernels(torch, size: dict, peak: dict):
                                                                   heads, head, page, 0.125, 0, chunk, -(-reach // chunk), acc, ml, counters))
             add(f"GPT-2 attention over split keys, {name}", us, bytes_moved=sum(lengths) * heads * head * 2 * 2.0, heads=heads)
     # ---- the matrix memories ----
-    for kind in ("mlstm", "lightning"):
+    for kind in memories:
         mem = size[kind]
         h, dim, vdim = mem["heads"], mem["dim"], mem["vdim"]
         gated = kind == "mlstm"
@@ -927,7 +927,7 @@ def sumozen_config(size: dict, vocab: int) -> dict:
             "layers": [three[i % 3] for i in range(size["layers"])]}
 
 
-def sumozen_kernels(torch, size: dict, peak: dict):
+def sumozen_kernels(torch, size: dict, peak: dict, recurrences=("right", "mamba"), experts=True):
     """Sumozen's kernels alone, replayed back to back on operands of their own: prompt portions
     (2 x 1,024 tokens) and single tokens (8 requests at 1,023 cached tokens), each with the work it
     must do and the fraction of its bound: 32-bit FMA (nominal) where the sums are 32-bit by the
@@ -986,7 +986,7 @@ def sumozen_kernels(torch, size: dict, peak: dict):
             add(f"capped attention, one block per (token, head), {name}", us, bytes_moved=sum(lengths) * kv_heads * (dim + vdim) * 2.0,
                 heads=heads, kv_heads=kv_heads, dim=dim)
     # ---- the recurrences ----
-    for kind in ("right", "mamba"):
+    for kind in recurrences:
         mem = size[kind]
         delta = kind == "right"
         h, vd = mem["heads"], mem["vdim"]
@@ -1012,6 +1012,8 @@ def sumozen_kernels(torch, size: dict, peak: dict):
                 add(f"{label}, token by token, {name}", us, flops=2.0 * 4 * kd * vd * h * n, heads=h, dim=kd, vdim=vd)
             else:
                 add(f"{label}, {name}", us, bytes_moved=2.0 * len(counts) * h * kd * vd * 4, heads=h, dim=kd, vdim=vd)
+    if not experts:
+        return lines
     # ---- the routed feed-forward ----
     moe, width = size["moe"], size["width"]
     experts, top, inner, shared = moe["experts"], moe["top"], moe["ff"], moe["shared"]
@@ -1114,6 +1116,16 @@ LIPULORN_SIZES = {
                "latent": {"heads": 16, "dim": 64, "rot_dim": 64, "vdim": 64, "kv_rank": 512, "q_rank": 512, "window": 512},
                "attention": {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 64, "chunk": 512},
                "delta": {"heads": 8, "kv_heads": 4, "dim": 128, "vdim": 128, "a_rank": 64, "g_rank": 64}},
+    # a wider one; the like stack and the like kernels' sizes are given here, the other designs' tables stop at 1,024
+    "large": {"width": 2048, "layers": 12, "ff": 5632, "streams": 4,
+              "latent": {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 1536, "window": 512},
+              "attention": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "chunk": 512},
+              "delta": {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "a_rank": 128, "g_rank": 128},
+              "fuvolix": {"width": 2048, "layers": 12, "ff": 8192,
+                          "latent": {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512},
+                          "mlstm": {"heads": 8, "dim": 128, "vdim": 256}, "lightning": {"heads": 16, "dim": 128, "vdim": 128}},
+              "sumozen": {"left": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128},
+                          "right": {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128}}},
 }
 
 
@@ -1285,8 +1297,10 @@ def run_compare_lipulorn(args):
     peak = peaks()
     context, vocab = 1024, GPT2_SMALL["vocab_size"]
     for name, size in LIPULORN_SIZES.items():
+        fuvolix = size["fuvolix"] if isinstance(size["fuvolix"], dict) else FUVOLIX_SIZES[size["fuvolix"]]
+        sumozen = size["sumozen"] if isinstance(size["sumozen"], dict) else SUMOZEN_SIZES[size["sumozen"]]
         for design in ("lipulorn", "fuvolix"):
-            raw = lipulorn_config(size, vocab) if design == "lipulorn" else fuvolix_config(FUVOLIX_SIZES[size["fuvolix"]], vocab)
+            raw = lipulorn_config(size, vocab) if design == "lipulorn" else fuvolix_config(fuvolix, vocab)
             with tempfile.TemporaryDirectory() as folder:
                 write_random_model(config_from_dict(raw), 0, folder, recipe="gpt2", store_dtype="bfloat16")
                 engine = Engine(folder, dtype="bfloat16", max_requests=16, cache_tokens=16 * context, max_tokens_per_step=2048,
@@ -1294,7 +1308,7 @@ def run_compare_lipulorn(args):
                 prefill_ms = prefill_run(engine, 2, 1024, vocab)
                 decode_ms, launches, _ = decode_run(engine, args.batch, args.steps, args.warmup, context, vocab)
                 print(json.dumps({"design": design, "size": name, "width": size["width"], "layers": size["layers"],
-                                  "inner": size["ff"] if design == "lipulorn" else FUVOLIX_SIZES[size["fuvolix"]]["ff"],
+                                  "inner": size["ff"] if design == "lipulorn" else fuvolix["ff"],
                                   "prefill_2048_tokens_ms": round(prefill_ms, 3), "prefill_tokens_per_s": round(2048 / prefill_ms * 1e3),
                                   "decode_batch": args.batch, "decode_ms_per_step": round(decode_ms, 3),
                                   "decode_tokens_per_s": round(args.batch / decode_ms * 1e3), "launches_per_decode_step": launches,
@@ -1303,12 +1317,11 @@ def run_compare_lipulorn(args):
                 torch.cuda.empty_cache()
         for line in lipulorn_kernels(torch, size, peak):
             print(json.dumps(dict(line, design="lipulorn", size=name)), flush=True)
-        for line in mixer_kernels(torch, FUVOLIX_SIZES[size["fuvolix"]], peak):
+        for line in mixer_kernels(torch, fuvolix, peak, memories=()):
             if line["kernel"].startswith("latent attention"):
                 print(json.dumps(dict(line, design="fuvolix", size=name)), flush=True)
-        for line in sumozen_kernels(torch, SUMOZEN_SIZES[size["sumozen"]], peak):
-            if line["kernel"].startswith(("capped attention", "gated delta rule")):
-                print(json.dumps(dict(line, design="sumozen", size=name)), flush=True)
+        for line in sumozen_kernels(torch, sumozen, peak, recurrences=("right",), experts=False):
+            print(json.dumps(dict(line, design="sumozen", size=name)), flush=True)
     return 0
 
 
