@@ -107,8 +107,8 @@ class LipulornConfig(ModelConfig):
         for index, layer in enumerate(listed):
             layers.append(read_layer(layer, index, layers))
         streams = _take(raw, "streams", int, "")
-        if streams > 8:
-            raise ConfigError(f"config key 'streams': at most 8 residual streams, got {streams}")
+        if streams > 16:
+            raise ConfigError(f"config key 'streams': at most 16 residual streams, got {streams}")
         return cls(architecture=architecture or raw.get("architecture") or "Lipulorn",
                    vocab=_take(raw, "vocab", int, ""), width=_take(raw, "width", int, ""), streams=streams,
                    norm_eps=_take(_section(raw, "norm"), "eps", float, "norm.", positive=False), layers=tuple(layers))

@@ -13,7 +13,7 @@
 
 MLLM_DEFINE_ERROR_API(mllm_streams)
 
-constexpr int MAX_STREAMS = 8;
+constexpr int MAX_STREAMS = 16;
 
 __global__ void streams_fill_kernel(float* __restrict__ streams, const float* __restrict__ hidden, int n_streams, int width,
                                     long n) {
@@ -37,14 +37,15 @@ extern "C" int mllm_streams_fill(float* streams, const float* hidden, int n_stre
 
 // VEC: 4 (every row starts on a 16-byte boundary and the width is a multiple of four: four columns a thread,
 // moved as one vector) or 1.  NS: the number of streams where it is known when compiled (1 to 4: the sums
-// unroll to what is needed and the kernel's registers allow more blocks an SM), or 0 for any number up to 8.
+// unroll to what is needed and the kernel's registers allow more blocks an SM), 0 for any number up to 8, -1 for
+// any number up to 16.
 template <typename T, int VEC, int NS>
 __global__ void __launch_bounds__(256)
 streams_step_kernel(float* __restrict__ streams, const float* __restrict__ y, long ld_y, const float* __restrict__ mix,
                     const float* __restrict__ w_out, int read, const float* __restrict__ w_in, float* __restrict__ u_out,
                     long ld_u, T* __restrict__ normed, long ld_normed, const float* __restrict__ gain, float eps, int n_streams,
                     int width) {
-    constexpr int BOUND = NS > 0 ? NS : MAX_STREAMS;
+    constexpr int BOUND = NS > 0 ? NS : (NS == 0 ? 8 : MAX_STREAMS);
     if (NS > 0) n_streams = NS;
     dependents_may_start();
     wait_for_earlier_kernels();
@@ -133,14 +134,15 @@ extern "C" int mllm_streams_step(float* streams, const float* y, long ld_y, cons
                                  const float* w_in, float* u_out, long ld_u, void* normed, long ld_normed, const float* gain,
                                  float eps, int n_streams, int width, int n_tokens, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
-    if (n_streams <= 0 || n_streams > MAX_STREAMS) return fail("streams_step: between 1 and 8 streams");
+    if (n_streams <= 0 || n_streams > MAX_STREAMS) return fail("streams_step: between 1 and 16 streams");
     if (width <= 0) return fail("streams_step: the width must be positive");
     if (y != nullptr && (mix == nullptr || w_out == nullptr)) return fail("streams_step: a sublayer result needs its mixing weights");
     if (normed != nullptr && (gain == nullptr || !read)) return fail("streams_step: the normed read-out needs a gain");
     const size_t shared = (size_t)width * sizeof(float);
     if (shared > 200 * 1024) return fail("streams_step: the row does not fit in shared memory");
     cudaStream_t s = (cudaStream_t)stream;
-    const bool vec = width % 4 == 0 && ((uintptr_t)streams & 15) == 0 &&
+    // (more than 8 streams: a column a thread, so that a thread's old streams stay in registers)
+    const bool vec = n_streams <= 8 && width % 4 == 0 && ((uintptr_t)streams & 15) == 0 &&
                      (y == nullptr || (((uintptr_t)y & 15) == 0 && ld_y % 4 == 0));
 #define LAUNCH_STREAMS_AS(T, VEC, NS)                                                                                            \
     do {                                                                                                                         \
@@ -156,7 +158,9 @@ extern "C" int mllm_streams_step(float* streams, const float* y, long ld_y, cons
         case 2: LAUNCH_STREAMS_AS(T, VEC, 2); break;                                                                             \
         case 3: LAUNCH_STREAMS_AS(T, VEC, 3); break;                                                                             \
         case 4: LAUNCH_STREAMS_AS(T, VEC, 4); break;                                                                             \
-        default: LAUNCH_STREAMS_AS(T, VEC, 0); break;                                                                            \
+        default:                                                                                                                 \
+            if (n_streams <= 8) LAUNCH_STREAMS_AS(T, VEC, 0); else LAUNCH_STREAMS_AS(T, 1, -1);                                  \
+            break;                                                                                                               \
         }                                                                                                                        \
     } while (0)
     if (dtype == DT_F32) {

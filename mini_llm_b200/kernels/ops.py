@@ -1400,7 +1400,7 @@ def scaled_add(x, u, a, v=None, b=0.0):
 _streams_fill = Function("streams", "mllm_streams_fill", [P, P, I, I, I, P])
 _streams_step = Function("streams", "mllm_streams_step", [P, P, L, P, P, I, P, P, L, P, L, P, F, I, I, I, I, P])
 _gated_act = Function("streams", "mllm_streams_gated_act", [P, L, P, L, I, I, I, I, P])
-MAX_STREAMS = 8
+MAX_STREAMS = 16
 GATED_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "none": 2}
 
 

@@ -47,8 +47,8 @@ class StreamConnection(Part):
     def __init__(self, prefix, n_streams: int, in_name: str = "in", out_name: str = "out", mix_name: str = "mix"):
         super().__init__(prefix)
         self.n_streams = int(n_streams)
-        if not 1 <= self.n_streams <= 8:
-            raise ValueError(f"{prefix}: between 1 and 8 streams, got {self.n_streams}")
+        if not 1 <= self.n_streams <= 16:
+            raise ValueError(f"{prefix}: between 1 and 16 streams, got {self.n_streams}")
         self.names = dict(read=in_name, write=out_name, mix=mix_name)
 
     def weight_specs(self):

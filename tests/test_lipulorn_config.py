@@ -42,7 +42,7 @@ def _with(raw, path, value):
 @pytest.mark.parametrize("change, named", [
     (lambda r: _without(r, ["vocab"]), "vocab"),
     (lambda r: _without(r, ["streams"]), "streams"),
-    (lambda r: _with(r, ["streams"], 9), "streams"),
+    (lambda r: _with(r, ["streams"], 17), "streams"),
     (lambda r: _without(r, ["norm", "eps"]), "norm.eps"),
     (lambda r: _with(r, ["layers", 0, "type"], "hyena"), "layers[0].type"),
     (lambda r: _without(r, ["layers", 0, "mixer", "kv_rank"]), "layers[0].mixer.kv_rank"),

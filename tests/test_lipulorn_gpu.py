@@ -55,9 +55,10 @@ def dev(values, dtype=torch.float32):
     (lp.delta(mlp=None, heads=6, kv_heads=2, dim=4, vdim=70, taps=2, a_rank=9, g_rank=2), 5),
     (lp.delta(mlp=lp.dense(7)), 8),
     (lp.attention(), 1),
+    (lp.latent(mlp=lp.dense(16)), 12),
 ], ids=["latent", "latent_one_head_window_of_one", "latent_wide_window_more_rotated_than_not", "attention",
         "attention_one_kv_head_blocks_of_one", "attention_one_block", "delta", "delta_one_head_one_tap_thin_ranks_of_one",
-        "delta_three_heads_a_key", "feed_forward_eight_streams", "feed_forward_one_stream"])
+        "delta_three_heads_a_key", "feed_forward_eight_streams", "feed_forward_one_stream", "feed_forward_twelve_streams"])
 def test_one_layer_of_each_kind(tmp_path, layer, streams):
     folder = lp.make_model(str(tmp_path / "m"), lp.config([layer], streams=streams), seed=3, matrix_scale=3.0)
     engine = engine_for(folder)

@@ -30,7 +30,7 @@ def scattered_table(lengths, page_size, seed=0):
 
 # ---- the residual streams ---------------------------------------------------------------------------
 
-@pytest.mark.parametrize("count, width, n", [(1, 24, 5), (3, 100, 33), (4, 768, 70), (8, 40, 2)])
+@pytest.mark.parametrize("count, width, n", [(1, 24, 5), (3, 100, 33), (4, 768, 70), (8, 40, 2), (6, 64, 9), (13, 52, 7), (16, 20, 3)])
 def test_streams_pass(count, width, n):
     from mini_llm_b200.kernels import ops
     rng = np.random.default_rng(count * 100 + width)
