@@ -32,7 +32,9 @@ class Workspace:
             capacity = max(rows, self.min_rows if held is None else 2 * held.shape[0])
             if tag == "logits":
                 capacity = rows if held is None else max(rows, held.shape[0])
-            held = torch.empty((capacity, *rest), dtype=dtype, device=self.device)
+            # zeros, not whatever the memory held: rows that a step's kernels leave unwritten (tokens that fill a step
+            # up to a round shape and are no tile's) are read by the kernels after them, and must be finite
+            held = torch.zeros((capacity, *rest), dtype=dtype, device=self.device)
             self._buffers[key] = held
             self.generation += 1
         return held[:rows]

@@ -91,6 +91,51 @@ def test_thin_ranks_are_read_off_the_tensors(tmp_path):
     check(engine_for(folder), folder, requests, schedule_portions(requests))
 
 
+def _random_stack(seed):
+    """A stack drawn at random: sizes, layer order, windows, blocks, taps, streams, which layers have a
+    feed-forward, and which latent layers read an earlier one's rows."""
+    rng = np.random.default_rng(1000 + seed)
+    pick = lambda values: values[int(rng.integers(0, len(values)))]
+    owners, layers = [], []
+    for index in range(int(rng.integers(2, 7))):
+        mlp = None if rng.random() < 0.3 else lp.dense(int(rng.integers(3, 50)))
+        kind = pick(["latent", "latent", "attention", "delta"])
+        if kind == "latent":
+            heads, dim, vdim, q_rank = int(rng.integers(1, 6)), pick([4, 8, 12, 20]), pick([4, 8, 12, 28]), int(rng.integers(2, 40))
+            window = int(rng.integers(1, 70))
+            if owners and rng.random() < 0.5:
+                source, kv_rank, rot_dim, base = pick(owners)
+                layers.append(lp.latent(heads, dim, rot_dim, vdim, kv_rank, q_rank, window, base, 1.0 / (dim + rot_dim), kv_from=source, mlp=mlp))
+            else:
+                kv_rank, rot_dim, base = pick([8, 12, 24, 40]), pick([2, 4, 8, 16]), pick([10.0, 500.0, 1e5])
+                owners.append((index, kv_rank, rot_dim, base))
+                layers.append(lp.latent(heads, dim, rot_dim, vdim, kv_rank, q_rank, window, base, 1.0 / (dim + rot_dim), mlp=mlp))
+        elif kind == "attention":
+            kv_heads = int(rng.integers(1, 4))
+            layers.append(lp.attention(kv_heads * int(rng.integers(1, 4)), kv_heads, pick([4, 8, 16, 20]), pick([4, 8, 16, 36]),
+                                       int(rng.integers(1, 70)), float(rng.uniform(0.2, 1.5)), mlp=mlp))
+        else:
+            kv_heads = int(rng.integers(1, 4))
+            layers.append(lp.delta(kv_heads * int(rng.integers(1, 3)), kv_heads, pick([4, 8, 12, 36]), pick([4, 8, 20, 33]), int(rng.integers(1, 6)),
+                                   int(rng.integers(1, 10)), int(rng.integers(1, 10)), mlp=mlp))
+    return lp.config(layers, width=pick([24, 40, 64, 100]), vocab=int(rng.integers(50, 300)), streams=int(rng.integers(1, 7)),
+                     eps=pick([1e-6, 1e-5, 1e-3]))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_stacks_drawn_at_random(tmp_path, seed):
+    """Whatever the configuration says is what runs: whole prompts, portions and mixed batches of a random stack."""
+    raw = _random_stack(seed)
+    folder = lp.make_model(str(tmp_path / "m"), raw, seed=seed, matrix_scale=2.5)
+    engine = engine_for(folder, max_requests=3, cache_tokens=320, debug_poison=True)
+    vocab = raw["vocab"]
+    requests = {"a": random_tokens(seed, 90, vocab), "b": random_tokens(seed + 50, 2, vocab), "c": random_tokens(seed + 99, 41, vocab)}
+    check(engine, folder, requests, schedule_whole(requests))
+    check(engine, folder, requests, schedule_portions(requests, sizes=(2, 9, 17, 3, 31)))
+    check(engine, folder, requests, schedule_mixed(requests, {"a": 60, "b": 1, "c": 30}, max_live=3))
+    assert not any(engine.cache.pages_in_use()) and engine.cache.free_slots == 3
+
+
 # ---- the same tokens, cut differently -----------------------------------------------------------
 
 def test_prompt_against_token_by_token_and_portions(tmp_path):
@@ -287,6 +332,30 @@ def test_bfloat16_with_sizes_no_fast_kernel_takes(tmp_path):
     check_rounding(engine, folder, requests, schedule_whole(requests))
     check_rounding(engine, folder, requests, schedule_mixed(requests, {"a": 130, "b": 2, "c": 33}, max_live=3))
     check(engine_for(folder), folder, requests, schedule_portions(requests))
+
+
+def test_nothing_depends_on_what_fresh_memory_holds(tmp_path):
+    """Steps with prompt portions are filled up to round shapes with tokens of no request; the rows of those
+    tokens that no attention tile takes are read by the kernels after them.  With every byte the engine gets
+    from the allocator full of NaN beforehand, and a first step that makes the buffers larger than the steps
+    after it need, no request's logits may change."""
+    from mini_llm_b200.engine import StepEntry
+    raw = lp.config([lp.latent(heads=3, dim=16, rot_dim=8, vdim=8, kv_rank=40, q_rank=40, window=166, mlp=None),
+                     lp.attention(heads=4, kv_heads=2, dim=48, vdim=8, chunk=180),
+                     lp.delta(heads=1, kv_heads=1, dim=8, vdim=20, taps=5, a_rank=24, g_rank=7, mlp=lp.dense(24)),
+                     lp.attention(heads=4, kv_heads=2, dim=32, vdim=36, chunk=14, mlp=lp.dense(100)),
+                     lp.attention(heads=4, kv_heads=2, dim=16, vdim=16, chunk=94, mlp=lp.dense(100))], width=256, vocab=352, streams=1)
+    folder = lp.make_model(str(tmp_path / "m"), raw, seed=15, bfloat16_values=True)
+    junk = [torch.full((size,), float("nan"), device="cuda") for size in (1 << 26, 1 << 24, 1 << 22, 1 << 20, 1 << 18, 1 << 16)
+            for _ in range(2)]
+    del junk
+    engine = engine_for(folder, dtype="bfloat16", page_size=16, max_requests=3)
+    slot = engine.open_request()
+    engine.step([StepEntry(slot, random_tokens(15, 300, 352), [299])], dump_hidden=True)       # runs as it is, not filled up
+    engine.close_request(slot)
+    requests = {"a": random_tokens(15, 300, 352), "b": random_tokens(65, 2, 352), "c": random_tokens(114, 150, 352)}
+    check_rounding(engine, folder, requests, schedule_whole(requests), share=0.06)
+    check_rounding(engine, folder, requests, schedule_mixed(requests, {"a": 260, "b": 1, "c": 100}, max_live=3), share=0.06)
 
 
 def test_greedy_generation_through_the_scheduler(tmp_path):
