@@ -111,10 +111,23 @@ class CacheStorage:
             owner = index if entry.cache_of is None else entry.cache_of
             writes = entry.cache_of is None
             roles = [key[1] for key in manager.entry_group if isinstance(key, tuple) and key[0] == owner]
+            # An entry that reads another's cache may still keep state of a fixed size of its own (a
+            # filter's last inputs): those views are its own and written; the owner's paged ones are read.
+            own = {}
+            if not writes:
+                own = {key[1]: view_of(key, True) for key in manager.entry_group if isinstance(key, tuple) and key[0] == index}
+                if index in manager.entry_group:
+                    own[None] = view_of(index, True)
+            if owner in manager.entry_group and own:
+                raise ValueError(f"run entry {index} keeps state of its own and reads the cache of entry {owner}, whose one cache "
+                                 f"has no name: the owner's part must name what it keeps (cache_need() -> {{name: need}})")
             if owner in manager.entry_group:
                 self.views.append(view_of(owner, writes))
-            elif roles:
-                self.views.append(CompositeLayerCache({role: view_of((owner, role), writes) for role in roles}))
+            elif roles or own:
+                by_role = {role: view_of((owner, role), writes) for role in roles
+                           if writes or manager.groups[manager.entry_group[(owner, role)][0]].paged}
+                by_role.update({role: view for role, view in own.items() if role is not None})
+                self.views.append(CompositeLayerCache(by_role))
             else:
                 self.views.append(LayerCache())
 

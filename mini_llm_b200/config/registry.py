@@ -66,4 +66,4 @@ def _load_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from ..models import fuvolix, gpt2, lipulorn, sumozen  # noqa: F401  (register themselves)
+        from ..models import deluvik, fuvolix, gpt2, lipulorn, sumozen  # noqa: F401  (register themselves)

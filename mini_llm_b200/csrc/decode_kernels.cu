@@ -229,9 +229,9 @@ split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
                        const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
                        const int* __restrict__ token_item, int n_heads, int n_kv_heads, int page_size, float scale,
-                       float cap, int window, int block, const float* __restrict__ gate, long ld_gate, int chunk,
-                       int max_chunks, float* __restrict__ part_acc, float* __restrict__ part_ml,
-                       int* __restrict__ counters) {
+                       float cap, int window, int block, const float* __restrict__ gate, long ld_gate,
+                       const float* __restrict__ sink, int chunk, int max_chunks, float* __restrict__ part_acc,
+                       float* __restrict__ part_ml, int* __restrict__ counters) {
     constexpr int LPK = D / 8;             // lanes per key: each lane owns 8 of the head's dimensions
     constexpr int KPW = 32 / LPK;          // keys per warp per step
     dependents_may_start();
@@ -375,7 +375,10 @@ split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
     const long first = ((long)t * n_heads + h) * max_chunks;
     float top = -INFINITY;
     for (int cc = c_first; cc <= c_last; cc++) top = fmaxf(top, __ldcg(part_ml + (first + cc) * 2));
-    float denom = 0.0f;
+    // a sink: one more term exp(sink[h]) in the denominator, with no key and no value (scores are in units of log2 e)
+    const float sink_log2 = sink != nullptr ? sink[h] * 1.4426950408889634f : -INFINITY;
+    top = fmaxf(top, sink_log2);
+    float denom = sink != nullptr ? exp2f(sink_log2 - top) : 0.0f;
     for (int cc = c_first; cc <= c_last; cc++)
         denom += __ldcg(part_ml + (first + cc) * 2 + 1) * exp2f(__ldcg(part_ml + (first + cc) * 2) - top);
     // a gate per (token, head) opens the result by its sigmoid
@@ -390,14 +393,15 @@ split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
 
 // (with a cap on the scores: score <- cap * tanh(score / cap); cap <= 0: none; with a mask of blocks of
 // positions: block > 0, a query sees only keys of its own block, counted from position 0; with a gate:
-// fp32 [tokens, >= heads], head h's result times sigmoid(gate[t, h]))
-extern "C" int mllm_decode_split_attention_masked(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,
-                                                  const void* v_pages, const int* block_table, int max_blocks,
-                                                  const int* positions, const int* token_item, int n_tokens, int n_heads,
-                                                  int n_kv_heads, int head_size, int page_size, float scale, float cap,
-                                                  int window, int block, const float* gate, long ld_gate, int chunk,
-                                                  int max_chunks, float* part_acc, float* part_ml, int* counters,
-                                                  void* stream) {
+// fp32 [tokens, >= heads], head h's result times sigmoid(gate[t, h]); with a sink: fp32 [heads], exp(sink[h]) joins
+// head h's softmax denominator)
+extern "C" int mllm_decode_split_attention_sink(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,
+                                                const void* v_pages, const int* block_table, int max_blocks,
+                                                const int* positions, const int* token_item, int n_tokens, int n_heads,
+                                                int n_kv_heads, int head_size, int page_size, float scale, float cap,
+                                                int window, int block, const float* gate, long ld_gate, const float* sink,
+                                                int chunk, int max_chunks, float* part_acc, float* part_ml, int* counters,
+                                                void* stream) {
     if (n_tokens <= 0) return 0;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
         return fail("split_attention: heads must be a multiple of key/value heads");
@@ -410,7 +414,7 @@ extern "C" int mllm_decode_split_attention_masked(void* out, long ld_out, const 
     launch_kernel(g_dependent_launch != 0, split_attention_kernel<D>, grid, dim3(128), 0, s, (bf16*)out, ld_out,     \
                   (const bf16*)q, ld_q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_blocks,         \
                   positions, token_item, n_heads, n_kv_heads, page_size, scale, cap, window, block, gate, ld_gate,   \
-                  chunk, max_chunks, part_acc, part_ml, counters)
+                  sink, chunk, max_chunks, part_acc, part_ml, counters)
     switch (head_size) {
     case 16: LAUNCH_SPLIT(16); break;
     case 32: LAUNCH_SPLIT(32); break;
@@ -421,6 +425,18 @@ extern "C" int mllm_decode_split_attention_masked(void* out, long ld_out, const 
     }
 #undef LAUNCH_SPLIT
     return check_launch("split_attention_kernel");
+}
+
+extern "C" int mllm_decode_split_attention_masked(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,
+                                                  const void* v_pages, const int* block_table, int max_blocks,
+                                                  const int* positions, const int* token_item, int n_tokens, int n_heads,
+                                                  int n_kv_heads, int head_size, int page_size, float scale, float cap,
+                                                  int window, int block, const float* gate, long ld_gate, int chunk,
+                                                  int max_chunks, float* part_acc, float* part_ml, int* counters,
+                                                  void* stream) {
+    return mllm_decode_split_attention_sink(out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions,
+                                            token_item, n_tokens, n_heads, n_kv_heads, head_size, page_size, scale, cap, window,
+                                            block, gate, ld_gate, nullptr, chunk, max_chunks, part_acc, part_ml, counters, stream);
 }
 
 extern "C" int mllm_decode_split_attention_capped(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,

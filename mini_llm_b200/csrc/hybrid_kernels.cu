@@ -187,7 +187,7 @@ capped_attention_plain_kernel(T* __restrict__ out, long ld_out, const T* __restr
                               const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
                               const int* __restrict__ token_item, int n_heads, int n_kv_heads, int dim, int vdim,
                               int page_size, float scale, float cap, int window, int chunk,
-                              const float* __restrict__ gate, long ld_gate) {
+                              const float* __restrict__ gate, long ld_gate, const float* __restrict__ sink) {
     dependents_may_start();
     wait_for_earlier_kernels();
     constexpr int R = CAP_MAX_HEAD / 32;
@@ -236,8 +236,10 @@ capped_attention_plain_kernel(T* __restrict__ out, long ld_out, const T* __restr
         if (d < vdim) sm_acc[warp][d] = acc[i];
     }
     __syncthreads();
-    const float big = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
-    float total = 0.0f, wgt[4];
+    float big = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+    // a sink: one more term exp(sink[h]) in the denominator, with no key and no value
+    if (sink != nullptr) big = fmaxf(big, sink[h]);
+    float total = sink != nullptr ? expf(sink[h] - big) : 0.0f, wgt[4];
 #pragma unroll
     for (int w = 0; w < 4; w++) {
         wgt[w] = sm_m[w] == -INFINITY ? 0.0f : expf(sm_m[w] - big);
@@ -286,7 +288,8 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
                               const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
                               const int* __restrict__ token_item, int n_tokens, int n_heads, int n_kv_heads, int dim,
                               int vdim, int page_size, float scale, float cap, int window, int chunk,
-                              const float* __restrict__ gate, long ld_gate, int tokens_per_block, int heads_per_block) {
+                              const float* __restrict__ gate, long ld_gate, const float* __restrict__ sink,
+                              int tokens_per_block, int heads_per_block) {
     dependents_may_start();
     wait_for_earlier_kernels();
     constexpr int ROWS = TILE_WARPS * R;
@@ -457,7 +460,14 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
         const int r = warp + s * TILE_WARPS;
         if (r >= n_rows) continue;
         const int token = first_token + r / n_heads_here, head = first_head + r % n_heads_here;
-        const float inv = (gate != nullptr ? sigmoid_f(gate[(long)token * ld_gate + head]) : 1.0f) / l[s];
+        float sum = l[s], shrink = 1.0f;
+        if (sink != nullptr) {
+            // the sink's term joins the denominator; the sums are rescaled if it is the largest
+            const float top = fmaxf(m[s], sink[head]);
+            shrink = expf(m[s] - top);
+            sum = sum * shrink + expf(sink[head] - top);
+        }
+        const float inv = (gate != nullptr ? sigmoid_f(gate[(long)token * ld_gate + head]) : 1.0f) * shrink / sum;
 #pragma unroll
         for (int i = 0; i < VPL; i++) {
             const int d = lane + 32 * i;
@@ -481,7 +491,7 @@ template <typename T, int R, int SIZE>
 static int launch_capped_tiles(void* out, long ld_out, const void* q, long ld_q, const void* k_pages, const void* v_pages,
                                const int* block_table, int max_blocks, const int* positions, const int* token_item, int n_tokens,
                                int n_heads, int n_kv_heads, int dim, int vdim, int page_size, float scale, float cap, int window,
-                               int chunk, const float* gate, long ld_gate, cudaStream_t s) {
+                               int chunk, const float* gate, long ld_gate, const float* sink, cudaStream_t s) {
     constexpr int ROWS = TILE_WARPS * R;
     const int group = n_heads / n_kv_heads;
     const int heads_per_block = group < ROWS ? group : ROWS;
@@ -495,8 +505,8 @@ static int launch_capped_tiles(void* out, long ld_out, const void* q, long ld_q,
     dim3 grid((n_tokens + tokens_per_block - 1) / tokens_per_block, n_kv_heads * chunks);
     launch_kernel(g_dependent_launch != 0, capped_attention_tiled_kernel<T, R, SIZE>, grid, dim3(TILE_WARPS * 32), shared, s, (T*)out,
                   ld_out, (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table, max_blocks, positions, token_item,
-                  n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, chunk, gate, ld_gate, tokens_per_block,
-                  heads_per_block);
+                  n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, chunk, gate, ld_gate, sink,
+                  tokens_per_block, heads_per_block);
     return check_launch("capped_attention_tiled_kernel");
 }
 
@@ -505,11 +515,11 @@ static int launch_capped_attention(bool tiled, void* out, long ld_out, const voi
                                    const void* v_pages, const int* block_table, int max_blocks, const int* positions,
                                    const int* token_item, int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim,
                                    int page_size, float scale, float cap, int window, int chunk, const float* gate, long ld_gate,
-                                   cudaStream_t s) {
+                                   const float* sink, cudaStream_t s) {
     if (!tiled) {
         launch_kernel(g_dependent_launch != 0, capped_attention_plain_kernel<T>, dim3(n_tokens, n_heads), dim3(128), 0, s, (T*)out,
                       ld_out, (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table, max_blocks, positions,
-                      token_item, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, chunk, gate, ld_gate);
+                      token_item, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, chunk, gate, ld_gate, sink);
         return check_launch("capped_attention_plain_kernel");
     }
     // rows a warp: four where the step has rows enough for the blocks to fill the GPU all the same
@@ -519,7 +529,7 @@ static int launch_capped_attention(bool tiled, void* out, long ld_out, const voi
     if (capped_tiled_shared(dim, vdim, per_warp) > 160 * 1024) per_warp = 2;
 #define TILES(R, SIZE)                                                                                                        \
     return launch_capped_tiles<T, R, SIZE>(out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions, token_item, \
-                                           n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, chunk, gate, ld_gate, s)
+                                           n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, chunk, gate, ld_gate, sink, s)
     const int size = (dim > vdim ? dim : vdim) <= 64 ? 64 : ((dim > vdim ? dim : vdim) <= 128 ? 128 : 256);
     if (per_warp == 4) { if (size == 64) TILES(4, 64); if (size == 128) TILES(4, 128); TILES(4, 256); }
     if (size == 64) TILES(2, 64);
@@ -532,7 +542,7 @@ extern "C" int mllm_hybrid_capped_attention(void* out, long ld_out, const void* 
                                             const void* v_pages, const int* block_table, int max_blocks, const int* positions,
                                             const int* token_item, int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim,
                                             int page_size, float scale, float cap, int window, int chunk, const float* gate,
-                                            long ld_gate, int tiled, int dtype, void* stream) {
+                                            long ld_gate, const float* sink, int tiled, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (dim <= 0 || dim > CAP_MAX_HEAD || vdim <= 0 || vdim > CAP_MAX_HEAD) return fail("capped_attention: key and value sizes must be in 1..256");
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return fail("capped_attention: heads must be a multiple of the key/value heads");
@@ -542,11 +552,11 @@ extern "C" int mllm_hybrid_capped_attention(void* out, long ld_out, const void* 
     if (dtype == DT_F32)
         return launch_capped_attention<float>(tiled != 0, out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions,
                                               token_item, n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, chunk, gate,
-                                              ld_gate, s);
+                                              ld_gate, sink, s);
     if (dtype == DT_BF16)
         return launch_capped_attention<bf16>(tiled != 0, out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions,
                                              token_item, n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, chunk, gate,
-                                             ld_gate, s);
+                                             ld_gate, sink, s);
     return fail("capped_attention: unknown dtype");
 }
 
@@ -885,7 +895,10 @@ extern "C" int mllm_hybrid_linear_recurrence(const RecurrenceParams* params, int
 //   route        per token: z = W_router x in 32-bit, s = sigmoid(z); the `top` experts with the
 //                largest s (the lower index wins a tie) with s as the weight of their INPUT; if
 //                there is a shared expert, one more pair: expert `n_experts`, input weight 1,
-//                output weight sigmoid(w_shared_gate . x)
+//                output weight sigmoid(w_shared_gate . x) (or 1 for a shared expert without a gate).
+//                With `softmax_of_chosen`: z (+ a bias per expert) itself ranks the experts, the
+//                chosen ones' OUTPUTS are weighed by the softmax over the chosen logits only, and
+//                their inputs by 1
 //   expert_up    act[pair, f] = silu(W_gate[e] x') * (W_up[e] x') with x' = weight * x
 //   expert_down  hidden[t] += sum over the token's pairs of out_weight * W_down[e] act[pair]
 // Experts are named by a table of pointers (gate, up, down) and inner sizes, so that experts of
@@ -922,9 +935,9 @@ __device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_c
 
 template <typename T>
 __global__ void __launch_bounds__(128)
-route_kernel(const T* __restrict__ x, long ld_x, const T* __restrict__ router, const T* __restrict__ shared_gate, int width,
-             int n_experts, int top, int pairs, int* __restrict__ choice, float* __restrict__ in_weight,
-             float* __restrict__ out_weight) {
+route_kernel(const T* __restrict__ x, long ld_x, const T* __restrict__ router, const float* __restrict__ router_bias,
+             const T* __restrict__ shared_gate, int shared_plain, int softmax_of_chosen, int width, int n_experts, int top,
+             int pairs, int* __restrict__ choice, float* __restrict__ in_weight, float* __restrict__ out_weight) {
     dependents_may_start();
     wait_for_earlier_kernels();
     extern __shared__ float shared[];
@@ -938,25 +951,39 @@ route_kernel(const T* __restrict__ x, long ld_x, const T* __restrict__ router, c
         float z = 0.0f;
         for (int c = lane; c < width; c += 32) z = fmaf(to_f32(w[c]), row[c], z);
         z = warp_sum(z);
-        if (lane == 0) score[e] = sigmoid_f(z);
+        if (e < n_experts && router_bias != nullptr) z += router_bias[e];
+        // (the chosen logits' softmax needs the logits themselves)
+        if (lane == 0) score[e] = softmax_of_chosen && e < n_experts ? z : sigmoid_f(z);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
+        float largest = 0.0f, total = 0.0f;
         for (int k = 0; k < top; k++) {
             int best = -1;
-            float best_score = -1.0f;
+            float best_score = -INFINITY;
             for (int e = 0; e < n_experts; e++)
                 if (score[e] > best_score) best = e, best_score = score[e];
             if (best < 0) best = 0, best_score = score[0];      // (scores that are no numbers)
             choice[(long)t * pairs + k] = best;
-            in_weight[(long)t * pairs + k] = best_score;
-            out_weight[(long)t * pairs + k] = 1.0f;
-            score[best] = -2.0f;
+            if (softmax_of_chosen) {
+                // weights of the outputs: the softmax over the chosen logits only (the first is the largest)
+                if (k == 0) largest = best_score;
+                const float e = expf(best_score - largest);
+                in_weight[(long)t * pairs + k] = 1.0f;
+                out_weight[(long)t * pairs + k] = e;
+                total += e;
+            } else {
+                in_weight[(long)t * pairs + k] = best_score;
+                out_weight[(long)t * pairs + k] = 1.0f;
+            }
+            score[best] = -INFINITY;
         }
-        if (shared_gate != nullptr) {
+        if (softmax_of_chosen)
+            for (int k = 0; k < top; k++) out_weight[(long)t * pairs + k] /= total;
+        if (shared_gate != nullptr || shared_plain) {
             choice[(long)t * pairs + top] = n_experts;
             in_weight[(long)t * pairs + top] = 1.0f;
-            out_weight[(long)t * pairs + top] = score[n_experts];
+            out_weight[(long)t * pairs + top] = shared_gate != nullptr ? score[n_experts] : 1.0f;
         }
     }
 }
@@ -1060,7 +1087,7 @@ expert_combine_kernel(T* __restrict__ act, long ld_act, const T* __restrict__ gu
             s = in_weight[(long)t * pairs + top], o = out_weight[(long)t * pairs + top];
         } else {
             for (int k = 0; k < top; k++)
-                if (choice[(long)t * pairs + k] == e) s = in_weight[(long)t * pairs + k];
+                if (choice[(long)t * pairs + k] == e) s = in_weight[(long)t * pairs + k], o = out_weight[(long)t * pairs + k];
         }
         float v = 0.0f;
         if (s != 0.0f) {
@@ -1090,20 +1117,24 @@ extern "C" int mllm_hybrid_expert_combine(void* act, long ld_act, const void* gu
     return check_launch("expert_combine_kernel");
 }
 
-extern "C" int mllm_hybrid_route(const void* x, long ld_x, const void* router, const void* shared_gate, int width, int n_experts,
-                                 int top, int* choice, float* in_weight, float* out_weight, int n_tokens, int dtype, void* stream) {
+extern "C" int mllm_hybrid_route(const void* x, long ld_x, const void* router, const float* router_bias, const void* shared_gate,
+                                 int shared_plain, int softmax_of_chosen, int width, int n_experts, int top, int* choice,
+                                 float* in_weight, float* out_weight, int n_tokens, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (top <= 0 || top > n_experts) return fail("route: every token takes between one and all experts");
+    if (shared_plain && shared_gate != nullptr) return fail("route: the shared expert has a gate or none");
     cudaStream_t s = (cudaStream_t)stream;
-    const int pairs = top + (shared_gate != nullptr ? 1 : 0);
+    const int pairs = top + (shared_gate != nullptr || shared_plain ? 1 : 0);
     const size_t shared = sizeof(float) * ((size_t)width + n_experts + 1);
     if (shared > 48 * 1024) return fail("route: the token and the scores do not fit shared memory");
     if (dtype == DT_F32)
         launch_kernel(g_dependent_launch != 0, route_kernel<float>, dim3(n_tokens), dim3(128), shared, s, (const float*)x, ld_x,
-                      (const float*)router, (const float*)shared_gate, width, n_experts, top, pairs, choice, in_weight, out_weight);
+                      (const float*)router, router_bias, (const float*)shared_gate, shared_plain, softmax_of_chosen, width,
+                      n_experts, top, pairs, choice, in_weight, out_weight);
     else if (dtype == DT_BF16)
         launch_kernel(g_dependent_launch != 0, route_kernel<bf16>, dim3(n_tokens), dim3(128), shared, s, (const bf16*)x, ld_x,
-                      (const bf16*)router, (const bf16*)shared_gate, width, n_experts, top, pairs, choice, in_weight, out_weight);
+                      (const bf16*)router, router_bias, (const bf16*)shared_gate, shared_plain, softmax_of_chosen, width,
+                      n_experts, top, pairs, choice, in_weight, out_weight);
     else
         return fail("route: unknown dtype");
     return check_launch("route_kernel");

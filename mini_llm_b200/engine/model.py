@@ -11,7 +11,7 @@ engine/src/gpt2_gpu.cu:254-263).
 from __future__ import annotations
 
 from ..parts.base import build_part, get_arrangement
-from ..parts.spec import NoCache
+from ..parts.spec import NoCache, PagedKV
 from ..parts.streams import read_sum
 from ..weights.loader import collect_specs, load_weights
 
@@ -61,9 +61,6 @@ class Model:
         needs = []
         for entry in self.spec.order:
             arrangement, parts = self.layers[entry.layer]
-            if entry.cache_of is not None:
-                needs.append(None)
-                continue
             mine = {}
             for role in arrangement.cache_roles(parts):
                 need = parts[role].cache_need()
@@ -73,9 +70,13 @@ class Model:
                 else:
                     mine[role] = need
             mine = {role: need for role, need in mine.items() if not isinstance(need, NoCache)}
+            if entry.cache_of is not None:
+                # the pages are the other entry's; state of a fixed size per request (a filter's last inputs) stays its own
+                mine = {role: need for role, need in mine.items() if not isinstance(need, PagedKV)}
             if not mine:
                 needs.append(None)
-            elif tuple(mine) == (arrangement.mixer_role(),) and tuple(arrangement.cache_roles(parts)) == tuple(mine):
+            elif (entry.cache_of is None and tuple(mine) == (arrangement.mixer_role(),)
+                  and tuple(arrangement.cache_roles(parts)) == tuple(mine)):
                 needs.append(mine[arrangement.mixer_role()])
             else:
                 needs.append(mine)
@@ -102,6 +103,7 @@ class Model:
                                           hidden.dtype)
             ctx.kernels.depth_mix(hidden, ctx.kept_results, None, 0)
         ctx.streams = ctx.streams_pending = None
+        ctx.rounded_stream = None        # the stream's rows in the activations' type, where an arrangement keeps them
         if self.spec.residual_streams > 0:
             # several residual streams, all equal to the embedding output at the start
             ctx.streams = ctx.buffer("streams", (ctx.n_tokens, self.spec.residual_streams, self.spec.hidden_size), hidden.dtype)

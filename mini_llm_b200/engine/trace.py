@@ -33,7 +33,7 @@ def parse_args(argv=None):
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     parser.add_argument("--page-size", type=int, default=16, help="tokens per cache page (a divisor of 64)")
-    parser.add_argument("--max-requests", type=int, default=8, help="most requests live at a time")
+    parser.add_argument("--max-requests", type=int, default=4, help="most requests live at a time (state slots)")
     parser.add_argument("--plain-kernels", action="store_true", help="run the plain kernel of every operation")
     return parser.parse_args(argv)
 

@@ -44,6 +44,7 @@ LIBRARIES = {
     "sequence": "sequence_kernels.cu",
     "hybrid": "hybrid_kernels.cu",
     "streams": "stream_kernels.cu",
+    "unit": "recurrent_unit_kernels.cu",
 }
 
 _lock = threading.Lock()

@@ -124,10 +124,11 @@ class Kernels:
                                    cache.block_table, cache.page_size, cache.k_pages, cache.v_pages, cache.writes)
 
     def capped_attention(self, ctx, out, q, cache, n_heads, n_kv_heads, dim, vdim, scale, cap=0.0, window=0, chunk=0,
-                         gate=None):
+                         gate=None, sink=None):
         """Attention whose weights stay 32-bit, with a cap on the scores and values of a size of
         their own; the mask is causal, over the last ``window`` positions or within blocks of
-        ``chunk`` positions; ``gate`` [T, heads] opens each head's result by its sigmoid.  Steps with
+        ``chunk`` positions; ``gate`` [T, heads] opens each head's result by its sigmoid; ``sink`` [heads] adds
+        exp(sink[h]) to head h's denominator.  Steps with
         prompt portions take the tiles (tokens of a request side by side share the cached rows they
         read); steps of single tokens, and sizes the tiles do not take, one block per (token, head)."""
         self.launches += 1
@@ -143,11 +144,11 @@ class Kernels:
             self.chose("capped_attention", "split_attention", n, n_heads, dim, vdim)
             return ops.split_attention(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.token_item,
                                        n_heads, n_kv_heads, dim, cache.page_size, scale, window, span, -(-reach // span), acc,
-                                       ml, counters, cap=cap, block=chunk, gate=gate)
+                                       ml, counters, cap=cap, block=chunk, gate=gate, sink=sink)
         tiled = not ctx.decode_only and ops.capped_attention_tiled_takes(dim, vdim, q.dtype)
         self.chose("capped_attention", "capped_attention_tiled" if tiled else "capped_attention_plain", q.shape[0], n_heads, dim, vdim)
         return ops.capped_attention(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.token_item,
-                                    n_heads, n_kv_heads, dim, vdim, cache.page_size, scale, cap, window, tiled, chunk, gate)
+                                    n_heads, n_kv_heads, dim, vdim, cache.page_size, scale, cap, window, tiled, chunk, gate, sink)
 
     def linear_recurrence(self, ctx, out, q, k, v, gate_a, gate_b, log_rate, step_bias, state, heads, qk_heads, dim, vdim,
                           delta, unit_norm=False, q_scale=1.0, skip=None, writes=True, channel_decay=False):
@@ -156,9 +157,10 @@ class Kernels:
                                      ctx.item_count, heads, qk_heads, dim, vdim, delta, unit_norm, q_scale, skip, writes,
                                      channel_decay)
 
-    def route(self, x, router, shared_gate, top, choice, in_weight, out_weight):
+    def route(self, x, router, shared_gate, top, choice, in_weight, out_weight, bias=None, softmax_of_chosen=False,
+              shared_plain=False):
         self.launches += 1
-        return ops.route(x, router, shared_gate, top, choice, in_weight, out_weight)
+        return ops.route(x, router, shared_gate, top, choice, in_weight, out_weight, bias, softmax_of_chosen, shared_plain)
 
     def experts(self, hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_of, inner_of, max_inner, pairs,
                 ld_down=None):
@@ -178,6 +180,28 @@ class Kernels:
     def expert_combine(self, act, gu, choice, in_weight, out_weight, n_experts, inner, top, pairs):
         self.launches += 1
         return ops.expert_combine(act, gu, choice, in_weight, out_weight, n_experts, inner, top, pairs)
+
+    # ---- norms on a sublayer's output, query and key norms with rotary positions, the gated linear recurrence ----
+    def norm_rotary_store(self, ctx, cache, qkv, q_out, k_off, v_off, heads, kv_heads, dim, vdim, q_gain, k_gain, norm, eps,
+                          rot_dims, layout, inv_freq):
+        self.launches += 1
+        writes = bool(cache.writes)
+        return ops.norm_rotary_store(qkv, k_off, v_off, heads, kv_heads, dim, vdim, q_out, q_gain, k_gain, norm, eps, rot_dims,
+                                     layout, inv_freq, ctx.positions, ctx.token_item, cache.block_table if writes else None,
+                                     cache.page_size, cache.k_pages if writes else None, cache.v_pages if writes else None, writes)
+
+    def gated_recurrence(self, ctx, out, u, y, gates, bias_r, bias_i, lam, decay_scale, state, block_width, writes=True):
+        self.launches += 1
+        return ops.gated_recurrence(out, u, y, gates, bias_r, bias_i, lam, decay_scale, state, ctx.item_slot, ctx.item_offset,
+                                    ctx.item_count, block_width, writes)
+
+    def add_normed_cast(self, hidden, y=None, gain=None, eps=0.0, act=None):
+        self.launches += 1
+        return ops.add_normed_cast(hidden, y, gain, eps, act)
+
+    def softcap(self, x, cap):
+        self.launches += 1
+        return ops.softcap(x, cap)
 
     def scaled_add(self, x, u, a, v=None, b=0.0):
         self.launches += 1

@@ -228,8 +228,8 @@ class _SkinnyParams(ctypes.Structure):
 
 
 _skinny = Function("decode", "mllm_decode_skinny_linear", [ctypes.POINTER(_SkinnyParams), P])
-_split_attention = Function("decode", "mllm_decode_split_attention_masked",
-                            [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, F, F, I, I, P, L, I, I, P, P, P, P])
+_split_attention = Function("decode", "mllm_decode_split_attention_sink",
+                            [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, F, F, I, I, P, L, P, I, I, P, P, P, P])
 
 SKINNY_MAX_SMEM = 200 * 1024
 SPLIT_ATTENTION_HEAD_SIZES = (16, 32, 64, 128, 256)
@@ -303,13 +303,14 @@ def skinny_linear(out, x, w, bias=None, epilogue="store", norm=None, scatter=Non
 
 
 def split_attention(out, q, k_pages, v_pages, block_table, positions, token_item, n_heads, n_kv_heads, head_size,
-                    page_size, scale, window, chunk, max_chunks, part_acc, part_ml, counters, cap=0.0, block=0, gate=None):
+                    page_size, scale, window, chunk, max_chunks, part_acc, part_ml, counters, cap=0.0, block=0, gate=None, sink=None):
     """Causal attention over the paged cache for few tokens: one CTA per (token, head, chunk
     of ``chunk`` keys); needs fp32 scratch ``part_acc`` [T*H*max_chunks*D], ``part_ml``
     [T*H*max_chunks*2] and zeroed int32 ``counters`` [T*H] (left zero).  ``cap`` > 0: the scores
     are capped, cap * tanh(score / cap).  ``block`` > 0: a query sees only the keys of its own block of
     ``block`` positions (blocks counted from position 0).  ``gate`` fp32 [T, >= heads]: head h's result
-    is multiplied by sigmoid(gate[t, h]).  Scores, weights and sums are 32-bit."""
+    is multiplied by sigmoid(gate[t, h]).  ``sink`` fp32 [heads]: exp(sink[h]) joins head h's denominator.
+    Scores, weights and sums are 32-bit."""
     _check(out, "split_attention.out", torch.bfloat16, 2)
     _check(q, "split_attention.q", torch.bfloat16, 2)
     _check(k_pages, "split_attention.k_pages", torch.bfloat16)
@@ -332,12 +333,20 @@ def split_attention(out, q, k_pages, v_pages, block_table, positions, token_item
         _check(gate, "split_attention.gate", torch.float32, 2)
         if gate.shape[0] < n or gate.shape[1] < n_heads or gate.stride(1) != 1:
             raise KernelError("split_attention: one gate per token and head")
+    _check_sink(sink, n_heads, "split_attention")
     _split_attention(out.data_ptr(), out.stride(0), q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
                      block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), token_item.data_ptr(), n,
                      n_heads, n_kv_heads, head_size, page_size, float(scale), float(cap or 0.0), int(window or 0), int(block or 0),
-                     _ptr(gate), gate.stride(0) if gate is not None else 0, int(chunk), int(max_chunks), part_acc.data_ptr(),
+                     _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(sink), int(chunk), int(max_chunks), part_acc.data_ptr(),
                      part_ml.data_ptr(), counters.data_ptr(), _stream())
     return out
+
+
+def _check_sink(sink, n_heads, who):
+    if sink is not None:
+        _check(sink, f"{who}.sink", torch.float32, 1)
+        if sink.shape[0] != n_heads:
+            raise KernelError(f"{who}: one sink per head")
 
 
 _group_attention = Function("decode", "mllm_decode_group_attention",
@@ -1192,7 +1201,7 @@ def rotary_store(qkv, k_off, v_off, heads, kv_heads, dim, vdim, rot_dims, inv_fr
 
 
 _capped_attention = Function("hybrid", "mllm_hybrid_capped_attention",
-                             [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, I, F, F, I, I, P, L, I, I, P])
+                             [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, I, F, F, I, I, P, L, P, I, I, P])
 
 
 def capped_attention_tiled_takes(dim, vdim, dtype=torch.bfloat16) -> bool:
@@ -1205,12 +1214,13 @@ def capped_attention_tiled_takes(dim, vdim, dtype=torch.bfloat16) -> bool:
 
 
 def capped_attention(out, q, k_pages, v_pages, block_table, positions, token_item, n_heads, n_kv_heads, dim, vdim,
-                     page_size, scale, cap=0.0, window=0, tiled=False, chunk=0, gate=None):
+                     page_size, scale, cap=0.0, window=0, tiled=False, chunk=0, gate=None, sink=None):
     """Causal attention of every token of the step over its request's pages, keys of ``dim`` and
     values of ``vdim`` entries per head, score = cap * tanh(q . k * scale / cap) (``cap`` 0: no cap);
     scores, weights and the weighted sum in 32-bit.  ``window`` > 0: the last ``window`` positions only;
     ``chunk`` > 0: only keys of the query's own block of ``chunk`` positions (blocks counted from
     position 0).  ``gate`` fp32 [T, >= heads]: head h's result is multiplied by sigmoid(gate[t, h]).
+    ``sink`` fp32 [heads]: the softmax's denominator also holds exp(sink[h]), a term with no key and no value.
     ``tiled``: consecutive tokens of a request share the cached rows they read (for steps with prompt
     portions)."""
     _check(out, "capped_attention.out", q.dtype, 2)
@@ -1227,10 +1237,12 @@ def capped_attention(out, q, k_pages, v_pages, block_table, positions, token_ite
         _check(gate, "capped_attention.gate", torch.float32, 2)
         if gate.shape[0] < n or gate.shape[1] < n_heads or gate.stride(1) != 1:
             raise KernelError("capped_attention: one gate per token and head")
+    _check_sink(sink, n_heads, "capped_attention")
     _capped_attention(out.data_ptr(), out.stride(0), q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
                       block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), token_item.data_ptr(), n, n_heads,
                       n_kv_heads, dim, vdim, page_size, float(scale), float(cap or 0.0), int(window or 0), int(chunk or 0),
-                      _ptr(gate), gate.stride(0) if gate is not None else 0, int(bool(tiled)), dtype_code(q.dtype), _stream())
+                      _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(sink), int(bool(tiled)), dtype_code(q.dtype),
+                      _stream())
     return out
 
 
@@ -1314,31 +1326,38 @@ def linear_recurrence(out, q, k, v, gate_a, gate_b, log_rate, step_bias, state, 
     return out
 
 
-_route = Function("hybrid", "mllm_hybrid_route", [P, L, P, P, I, I, I, P, P, P, I, I, P])
+_route = Function("hybrid", "mllm_hybrid_route", [P, L, P, P, P, I, I, I, I, I, P, P, P, I, I, P])
 _experts = Function("hybrid", "mllm_hybrid_experts", [P, L, P, L, P, L, P, P, P, P, P, P, P, L, I, I, I, I, I, P])
 _expert_combine = Function("hybrid", "mllm_hybrid_expert_combine", [P, L, P, L, P, P, P, I, I, I, I, I, I, I, P])
 
 
-def route(x, router, shared_gate, top, choice, in_weight, out_weight):
+def route(x, router, shared_gate, top, choice, in_weight, out_weight, bias=None, softmax_of_chosen=False, shared_plain=False):
     """Per row of ``x``: sigmoid scores of ``router`` [experts, width] (sums in 32-bit), the ``top``
     largest with their scores as input weights; with ``shared_gate`` [1, width] one more pair per
-    token: expert ``experts``, input weight 1, output weight sigmoid(shared_gate . x).
-    choice int32, in_weight / out_weight fp32: [T * pairs]."""
+    token: expert ``experts``, input weight 1, output weight sigmoid(shared_gate . x); ``shared_plain``:
+    that pair with output weight 1 and no gate.  ``softmax_of_chosen``: the logits (plus ``bias`` fp32
+    [experts]) rank the experts, and the chosen ones get input weight 1 and, as output weight, the
+    softmax over the chosen logits only.  choice int32, in_weight / out_weight fp32: [T * pairs]."""
     _check(x, "route.x", None, 2)
     _check(router, "route.router", x.dtype, 2)
     _check(choice, "route.choice", torch.int32, 1)
     _check(in_weight, "route.in_weight", torch.float32, 1)
     _check(out_weight, "route.out_weight", torch.float32, 1)
     n, width = x.shape
-    pairs = top + (1 if shared_gate is not None else 0)
+    pairs = top + (1 if shared_gate is not None or shared_plain else 0)
     if router.shape[1] != width or not router.is_contiguous() or min(choice.shape[0], in_weight.shape[0], out_weight.shape[0]) < n * pairs:
         raise KernelError("route: sizes do not agree")
+    if bias is not None:
+        _check(bias, "route.bias", torch.float32, 1)
+        if bias.shape[0] != router.shape[0]:
+            raise KernelError("route: one bias per expert")
     if shared_gate is not None:
         _check(shared_gate, "route.shared_gate", x.dtype)
         if shared_gate.numel() != width or not shared_gate.is_contiguous():
             raise KernelError("route: the shared expert's gate is one row of the width")
-    _route(x.data_ptr(), x.stride(0), router.data_ptr(), _ptr(shared_gate), width, router.shape[0], top, choice.data_ptr(),
-           in_weight.data_ptr(), out_weight.data_ptr(), n, dtype_code(x.dtype), _stream())
+    _route(x.data_ptr(), x.stride(0), router.data_ptr(), _ptr(bias), _ptr(shared_gate), int(bool(shared_plain)),
+           int(bool(softmax_of_chosen)), width, router.shape[0], top, choice.data_ptr(), in_weight.data_ptr(),
+           out_weight.data_ptr(), n, dtype_code(x.dtype), _stream())
 
 
 def experts(hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_of, inner_of, max_inner, pairs, ld_down=None):
@@ -1457,3 +1476,114 @@ def gated_act(out, gu, activation="silu"):
     _gated_act(out.data_ptr(), out.stride(0), gu.data_ptr(), gu.stride(0), inner, GATED_ACTIVATIONS[activation], n,
                dtype_code(gu.dtype), _stream())
     return out
+
+
+# ---- norms on a sublayer's output, query and key norms with rotary positions, gated linear recurrence ----
+
+_norm_rotary_store = Function("unit", "mllm_unit_norm_rotary_store",
+                              [P, L, I, I, I, I, I, I, P, L, P, P, I, F, I, I, P, P, P, P, I, I, P, P, I, I, I, P])
+_gated_recurrence = Function("unit", "mllm_unit_gated_recurrence",
+                             [P, L, P, L, P, L, P, L, P, P, P, F, P, L, P, P, P, I, I, I, I, I, I, P])
+_add_normed_cast = Function("unit", "mllm_unit_add_normed_cast", [P, P, P, F, P, I, I, I, P])
+_softcap = Function("unit", "mllm_unit_softcap", [P, F, L, P])
+QK_NORMS = {None: 0, "none": 0, "whole": 1, "head": 2}
+
+
+def norm_rotary_store(qkv, k_off, v_off, heads, kv_heads, dim, vdim, q_out, q_gain, k_gain, norm, eps, rot_dims, layout, inv_freq,
+                      positions, token_item, block_table, page_size, k_pages, v_pages, writes=True):
+    """Rows of the fp32 ``qkv`` hold the projected [q | k | v] (k from column ``k_off``, v from ``v_off``; ``v_off`` may
+    equal ``k_off``: the values are then the keys as projected).  ``norm`` "whole": q and k are divided by the root mean
+    square of their whole projection and multiplied by ``q_gain`` [heads * dim] / ``k_gain`` [kv_heads * dim]; "head":
+    every head by its own, times a gain of ``dim`` entries shared by the heads; None: no norm.  Then the first
+    ``rot_dims`` entries of every head turn by position * ``inv_freq`` [rot_dims / 2] (float64) in pairs that are
+    neighbours (``layout`` "interleaved") or half the rotated entries apart ("half").  Queries go to ``q_out``
+    [T, heads * dim]; keys and values to the token's place in the pages (unless ``writes`` is false: then only
+    the queries are made and the pages may be None)."""
+    _check(qkv, "norm_rotary_store.qkv", torch.float32, 2)
+    _check(q_out, "norm_rotary_store.q_out", None, 2)
+    _check(inv_freq, "norm_rotary_store.inv_freq", torch.float64, 1)
+    n = qkv.shape[0]
+    mode = QK_NORMS[norm]
+    if q_out.shape != (n, heads * dim) or inv_freq.shape[0] < max(rot_dims // 2, 1) or heads * dim > qkv.shape[1]:
+        raise KernelError("norm_rotary_store: sizes do not agree")
+    gain_size = {0: None, 1: (heads * dim, kv_heads * dim), 2: (dim, dim)}[mode]
+    if mode:
+        _check(q_gain, "norm_rotary_store.q_gain", torch.float32, 1)
+        if q_gain.shape[0] != gain_size[0]:
+            raise KernelError(f"norm_rotary_store: the queries' gain has {q_gain.shape[0]} entries, not {gain_size[0]}")
+    if writes:
+        _check(k_pages, "norm_rotary_store.k_pages", q_out.dtype)
+        _check(v_pages, "norm_rotary_store.v_pages", q_out.dtype)
+        _check(block_table, "norm_rotary_store.block_table", torch.int32, 2)
+        if mode:
+            _check(k_gain, "norm_rotary_store.k_gain", torch.float32, 1)
+            if k_gain.shape[0] != gain_size[1]:
+                raise KernelError(f"norm_rotary_store: the keys' gain has {k_gain.shape[0]} entries, not {gain_size[1]}")
+        if v_off + kv_heads * vdim > qkv.shape[1] or k_off + kv_heads * dim > qkv.shape[1]:
+            raise KernelError("norm_rotary_store: keys or values lie outside the row")
+        if (not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous()
+                or k_pages.numel() % (page_size * kv_heads * dim) != 0 or v_pages.numel() % (page_size * kv_heads * vdim) != 0):
+            raise KernelError("norm_rotary_store: the pages do not hold whole pages of these rows")
+    _norm_rotary_store(qkv.data_ptr(), qkv.stride(0), int(k_off), int(v_off), heads, kv_heads, dim, vdim, q_out.data_ptr(),
+                       q_out.stride(0), _ptr(q_gain) if mode else None, _ptr(k_gain) if mode and writes else None, mode, float(eps),
+                       int(rot_dims), ROTARY_LAYOUTS[layout], inv_freq.data_ptr(), positions.data_ptr(), token_item.data_ptr(),
+                       block_table.data_ptr() if writes else None, block_table.shape[1] if writes else 0, page_size,
+                       k_pages.data_ptr() if writes else None, v_pages.data_ptr() if writes else None, int(bool(writes)), n,
+                       dtype_code(q_out.dtype), _stream())
+    return q_out
+
+
+def gated_recurrence(out, u, y, gates, bias_r, bias_i, lam, decay_scale, state, item_slot, item_offset, item_count, block_width,
+                     writes=True):
+    """Per channel c: S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t with a_t = exp(-decay_scale * r_t * softplus(lam[c])),
+    r_t = sigmoid(gate_r + bias_r[c]), i_t = sigmoid(gate_i + bias_i[c]); out_t = S_t * gelu_tanh(y_t).  ``gates`` fp32
+    [T, 2 * inner]: for every block of ``block_width`` channels its r gates, then its i gates.  ``state`` fp32
+    [slots, inner] holds S per request and is moved on (unless ``writes`` is false)."""
+    _check(out, "gated_recurrence.out", u.dtype, 2)
+    _check(u, "gated_recurrence.u", None, 2)
+    _check(y, "gated_recurrence.y", u.dtype, 2)
+    _check(gates, "gated_recurrence.gates", torch.float32, 2)
+    _check(state, "gated_recurrence.state", torch.float32, 2)
+    for name, t in (("bias_r", bias_r), ("bias_i", bias_i), ("lam", lam)):
+        _check(t, f"gated_recurrence.{name}", torch.float32, 1)
+    for name, t in (("item_slot", item_slot), ("item_offset", item_offset), ("item_count", item_count)):
+        _check(t, f"gated_recurrence.{name}", torch.int32, 1)
+    n, inner = out.shape
+    if (u.shape != (n, inner) or y.shape != (n, inner) or gates.shape != (n, 2 * inner) or state.shape[1] != inner
+            or min(bias_r.shape[0], bias_i.shape[0], lam.shape[0]) < inner or inner % block_width != 0):
+        raise KernelError("gated_recurrence: sizes do not agree")
+    _gated_recurrence(out.data_ptr(), out.stride(0), u.data_ptr(), u.stride(0), y.data_ptr(), y.stride(0), gates.data_ptr(),
+                      gates.stride(0), bias_r.data_ptr(), bias_i.data_ptr(), lam.data_ptr(), float(decay_scale), state.data_ptr(),
+                      state.stride(0), item_slot.data_ptr(), item_offset.data_ptr(), item_count.data_ptr(), inner, int(block_width),
+                      int(bool(writes)), item_count.shape[0], n, dtype_code(u.dtype), _stream())
+    return out
+
+
+def add_normed_cast(hidden, y=None, gain=None, eps=0.0, act=None):
+    """hidden += y / sqrt(mean(y^2) + eps) * gain on the fp32 stream (``y`` None: nothing is added), and the rows as they
+    then are, rounded, to ``act`` (None: not kept)."""
+    _check(hidden, "add_normed_cast.hidden", torch.float32, 2)
+    n, width = hidden.shape
+    if not hidden.is_contiguous():
+        raise KernelError("add_normed_cast: the stream must be contiguous")
+    if y is not None:
+        _check(y, "add_normed_cast.y", torch.float32, 2)
+        _check(gain, "add_normed_cast.gain", torch.float32, 1)
+        if y.shape[0] < n or y.shape[1] != width or not y.is_contiguous() or gain.shape[0] != width:
+            raise KernelError("add_normed_cast: the sublayer's result or the gain has another shape")
+    if act is not None:
+        _check(act, "add_normed_cast.act", None, 2)
+        if act.shape != (n, width) or not act.is_contiguous():
+            raise KernelError("add_normed_cast: the rounded rows have another shape")
+    _add_normed_cast(hidden.data_ptr(), _ptr(y), _ptr(gain), float(eps), _ptr(act), width, n,
+                     dtype_code(act.dtype) if act is not None else DT_F32, _stream())
+    return hidden
+
+
+def softcap(x, cap):
+    """x <- cap * tanh(x / cap), fp32, in place."""
+    _check(x, "softcap.x", torch.float32)
+    if not x.is_contiguous():
+        raise KernelError("softcap: the rows must be contiguous")
+    _softcap(x.data_ptr(), float(cap), x.numel(), _stream())
+    return x

@@ -277,6 +277,124 @@ class GatedAttention(Mixer):
         ctx.kernels.scaled_add(hidden, self.compute(ctx, x, cache), 1.0)
 
 
+class NormedAttention(Mixer):
+    """Causal attention whose queries and keys are normed before their rotary positions, with an optional sink.
+
+    ``q = W_q x``, ``k = W_k x`` and, with ``values="projected"``, ``v = W_v x`` (one product over the stacked
+    matrices, left in 32-bit; no biases); with ``values="keys"`` there is no W_v and the values are the keys as
+    projected, before norm and rotation.  With ``taps`` > 1 every channel of q, k and v then passes a short causal
+    convolution, ``y_t = sum_j w[:, j] u_(t - taps + 1 + j)`` (no bias; the last ``taps - 1`` projected rows of a
+    request are its state).  ``norm="whole"``: q (and k) are divided by the root mean square of the whole
+    projection, all heads at once, and multiplied by a gain of that size; ``norm="head"``: every head by its
+    own, times one gain of the head's size that all heads share; eps inside the root.  Then the position
+    encoding (``position``: a part with ``norm_rotate_store``) turns q and k, and the keys and values go to the
+    pages.  ``score = q . k * scale``, with ``softcap`` ``cap * tanh(score / cap)``, over the keys at positions <= the
+    query's (of those the last ``window`` if given); with ``sink`` the softmax's denominator also holds
+    ``exp(sink[h])``, a learned number per head that has no key and no value; softmax and the weighted sum in
+    32-bit; query head h reads key/value head ``h // (heads / kv_heads)``; then ``W_o``.  ``own_kv=False``: the part
+    has no keys and values (no projections, taps or norm of them): it attends, with its own queries, over the
+    pages of the run entry named by ``RunEntry.cache_of``."""
+
+    graph_safe = True
+
+    def __init__(self, prefix, width: int, n_heads: int, n_kv_heads: int, key_size: int, value_size: int, score_scale: float,
+                 eps: float, position, norm: str | None = "whole", values: str = "projected", taps: int = 1,
+                 softcap: float | None = None, window: int | None = None, sink: bool = False, own_kv: bool = True,
+                 names: dict | None = None):
+        super().__init__(prefix)
+        self.width, self.n_heads, self.n_kv_heads = int(width), int(n_heads), int(n_kv_heads)
+        self.dim, self.vdim, self.taps = int(key_size), int(value_size), int(taps)
+        self.score_scale, self.eps = float(score_scale), float(eps)
+        self.softcap = float(softcap) if softcap else 0.0
+        self.window = int(window) if window else None
+        self.sink, self.own_kv = bool(sink), bool(own_kv)
+        if min(self.n_heads, self.n_kv_heads, self.dim, self.vdim) <= 0 or self.n_heads % self.n_kv_heads != 0:
+            raise ValueError(f"{prefix}: {self.n_heads} heads are not a positive multiple of {self.n_kv_heads} key/value heads")
+        if norm not in (None, "whole", "head"):
+            raise ValueError(f"{prefix}: unknown query and key norm '{norm}' (known: head, whole)")
+        if values not in ("projected", "keys"):
+            raise ValueError(f"{prefix}: the values are 'projected' or the 'keys', got '{values}'")
+        if values == "keys" and self.vdim != self.dim:
+            raise ValueError(f"{prefix}: values that are the keys have the keys' size {self.dim}, not {self.vdim}")
+        if self.taps < 1:
+            raise ValueError(f"{prefix}: a convolution has at least one tap")
+        self.norm, self.values = norm, values
+        self.position = build_part(position)
+        if not hasattr(self.position, "norm_rotate_store"):
+            raise ValueError(f"{prefix}: the position encoding '{position.kind}' has no norm_rotate_store(ctx, cache, qkv, ...)")
+        self.names = dict(q="q", k="k", v="v", o="o", norm=".norm", taps=".conv", sink="sink")
+        self.names.update(names or {})
+        self.q_width, self.k_width, self.v_width = self.n_heads * self.dim, self.n_kv_heads * self.dim, self.n_kv_heads * self.vdim
+        self.projections = [("q", self.q_width)]
+        if self.own_kv:
+            self.projections.append(("k", self.k_width))
+            if values == "projected":
+                self.projections.append(("v", self.v_width))
+        self.proj_width = sum(rows for _, rows in self.projections)
+
+    def weight_specs(self):
+        n = self.names
+        specs = list(self.position.weight_specs())
+        for key, rows in self.projections:
+            specs.append(WeightSpec(self.full_name(n[key]), (rows, self.width)))
+            if self.taps > 1:
+                specs.append(WeightSpec(self.full_name(n[key] + n["taps"]), (rows, self.taps), role="vector", init="matrix"))
+            if self.norm is not None and key != "v":
+                specs.append(WeightSpec(self.full_name(n[key] + n["norm"]), (rows if self.norm == "whole" else self.dim,),
+                                        role="vector", init="gain"))
+        if self.sink:
+            specs.append(WeightSpec(self.full_name(n["sink"]), (self.n_heads,), role="vector", init="shift"))
+        specs.append(WeightSpec(self.full_name(n["o"]), (self.width, self.n_heads * self.vdim), init="residual_matrix"))
+        return specs
+
+    def cache_need(self):
+        # (an entry that reads another's pages gets them under the same name, "kv")
+        need = {"kv": PagedKV(self.n_kv_heads, self.dim, self.window, value_size=self.vdim)}
+        if self.taps > 1:
+            need["taps"] = FixedState((self.taps - 1, self.proj_width), "float32")
+        return need
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        n = self.names
+        self.position.bind({w.name: tensors[w.name] for w in self.position.weight_specs() if w.name in tensors}, runtime)
+        keys = [key for key, _ in self.projections]
+        self.stacked = torch.cat([self.w(n[key]) for key in keys]).contiguous()
+        self.stacked_taps = torch.cat([self.w(n[key] + n["taps"]) for key in keys]).contiguous() if self.taps > 1 else None
+        self.q_gain = self.w(n["q"] + n["norm"]) if self.norm is not None else None
+        self.k_gain = self.w(n["k"] + n["norm"]) if self.norm is not None and self.own_kv else None
+
+    def compute(self, ctx, x, cache):
+        k, n = ctx.kernels, x.shape[0]
+        pages = cache.of("kv")
+        if self.own_kv != bool(pages.writes):
+            raise RuntimeError(f"{self.prefix}: a part {'with' if self.own_kv else 'without'} keys and values of its own got pages "
+                               f"it may {'not ' if self.own_kv else ''}store into (RunEntry.cache_of)")
+        # projections, taps, norm and rotation in 32-bit: the queries and the cache are rounded once
+        projected = ctx.buffer("qkv_32", (n, self.proj_width), torch.float32)
+        k.linear(ctx, projected, x, self.stacked)
+        if self.taps > 1:
+            held = cache.of("taps")
+            filtered = ctx.buffer("qkv_32_filtered", (n, self.proj_width), torch.float32)
+            k.causal_taps(ctx, filtered, projected, self.stacked_taps, held.state, held.writes, identity=False)
+            projected = filtered
+        q = ctx.buffer("q", (n, self.q_width), ctx.act_dtype)
+        k_off = self.q_width
+        v_off = k_off + self.k_width if self.values == "projected" else k_off
+        self.position.norm_rotate_store(ctx, pages, projected, q, k_off, v_off, self.n_heads, self.n_kv_heads, self.dim, self.vdim,
+                                        self.q_gain, self.k_gain, self.norm, self.eps)
+        mixed = ctx.buffer("attn_out", (n, self.n_heads * self.vdim), ctx.act_dtype)
+        k.capped_attention(ctx, mixed, q, pages, self.n_heads, self.n_kv_heads, self.dim, self.vdim, self.score_scale,
+                           self.softcap, self.window or 0, sink=self.w(self.names["sink"]) if self.sink else None)
+        out = ctx.buffer("mixer_out", (n, self.width), torch.float32)
+        k.linear(ctx, out, mixed, self.w(self.names["o"]))
+        return out
+
+    def forward(self, ctx, x, hidden, cache):
+        ctx.kernels.scaled_add(hidden, self.compute(ctx, x, cache), 1.0)
+
+
 register_part("causal_self_attention", CausalSelfAttention)
+register_part("normed_attention", NormedAttention)
 register_part("filtered_attention", FilteredAttention)
 register_part("gated_attention", GatedAttention)

@@ -11,6 +11,10 @@ x by a weighted sum of all layer results so far.  The input filter (a short conv
 the feed-forward are optional roles; the mixer and the feed-forward hand over their output itself
 (``compute``), and the outer norm adds it onto the stream (``add_normed``).
 
+"output_norm" norms a sublayer's OUTPUT only: ``x <- x + norm_1(mixer(x))``, then, if the layer has a feed-forward,
+``x <- x + norm_2(feed_forward(x))``.  The sublayers read the stream itself, rounded to the activations' type; the
+rounded rows are written by the pass that adds the normed result before them (the first layer rounds by itself).
+
 "hyper_connections" is the pre-norm block over several residual streams (``ctx.streams``; see
 ``parts.streams``): each sublayer reads a weighted sum of the streams through its norm and writes
 its result back onto all of them through a mixing matrix.  ``hidden`` is not touched; the model
@@ -67,6 +71,36 @@ class SandwichNorm(Arrangement):
             parts["depth_mix"].forward(ctx, hidden)
 
 
+class OutputNorm(Arrangement):
+    roles = ("mixer", "norm_1")
+    optional_roles = ("feed_forward", "norm_2")     # a layer may have no feed-forward
+
+    @staticmethod
+    def _stream(ctx, hidden):
+        """What a sublayer reads: the 32-bit stream itself, or its rows rounded to the activations' type."""
+        if ctx.act_dtype == hidden.dtype:
+            return hidden
+        if getattr(ctx, "rounded_stream", None) is None:
+            ctx.rounded_stream = ctx.buffer("stream_rounded", tuple(hidden.shape), ctx.act_dtype)
+            ctx.kernels.add_normed_cast(hidden, act=ctx.rounded_stream)
+        return ctx.rounded_stream
+
+    @staticmethod
+    def _add(ctx, norm, hidden, y):
+        if ctx.act_dtype == hidden.dtype:
+            norm.add_normed(ctx, hidden, y)
+        else:
+            ctx.rounded_stream = ctx.buffer("stream_rounded", tuple(hidden.shape), ctx.act_dtype)
+            norm.add_normed(ctx, hidden, y, rounded=ctx.rounded_stream)
+
+    def run(self, ctx, parts, hidden, cache):
+        if getattr(cache, "kind", "none") == "composite":
+            cache = cache.sub("mixer")
+        self._add(ctx, parts["norm_1"], hidden, parts["mixer"].compute(ctx, self._stream(ctx, hidden), cache))
+        if "feed_forward" in parts:
+            self._add(ctx, parts["norm_2"], hidden, parts["feed_forward"].compute(ctx, self._stream(ctx, hidden)))
+
+
 class HyperConnections(Arrangement):
     roles = ("streams_1", "norm_1", "mixer")
     optional_roles = ("streams_2", "norm_2", "feed_forward")     # a layer may have no feed-forward
@@ -88,5 +122,6 @@ class HyperConnections(Arrangement):
 
 
 register_arrangement("pre_norm", PreNorm())
+register_arrangement("output_norm", OutputNorm())
 register_arrangement("hyper_connections", HyperConnections())
 register_arrangement("sandwich_norm", SandwichNorm())

@@ -55,12 +55,14 @@ class LearnedPositions(PositionEncoding):
 
 class LinearHead(Head):
     """logits = x W^T, W [vocab, width].  ``weight_name`` may be the token
-    table's name (tied head): the loader then shares the one tensor."""
+    table's name (tied head): the loader then shares the one tensor.  With ``softcap`` the logits are
+    then capped, ``cap * tanh(logits / cap)``."""
     graph_safe = True
 
-    def __init__(self, prefix, vocab_size: int, width: int, weight_name: str = "lm_head.weight"):
+    def __init__(self, prefix, vocab_size: int, width: int, weight_name: str = "lm_head.weight", softcap: float | None = None):
         super().__init__(prefix)
         self.vocab_size, self.width, self.weight_name = int(vocab_size), int(width), weight_name
+        self.softcap = float(softcap) if softcap else None      # logits <- cap * tanh(logits / cap)
 
     def weight_specs(self):
         return [WeightSpec(self.full_name(self.weight_name), (self.vocab_size, self.width), role="table", init="table")]
@@ -70,6 +72,8 @@ class LinearHead(Head):
     def forward(self, ctx, x):
         logits = ctx.buffer("logits", (x.shape[0], self.vocab_size), torch.float32)
         ctx.kernels.linear(ctx, logits, x, self.w(self.weight_name), None)
+        if self.softcap is not None:
+            ctx.kernels.softcap(logits, self.softcap)
         return logits
 
 

@@ -7,6 +7,11 @@ the stream, with ``expert(u) = W_down (silu(W_gate u) * (W_up u))`` and no biase
 the same form (with an inner size of its own) may run for every token; its output is multiplied
 by ``sigmoid(w_sg . x)``, one number per token.
 
+``weights="softmax_of_chosen"`` is the other common rule: the logits themselves (plus ``router_bias``, one number per
+expert, if the model has one) rank the experts, the chosen experts' OUTPUTS are weighed by the softmax over the
+chosen logits only, and their inputs are the token itself.  ``shared_gate=False``: the shared expert has no
+gate and is simply added.
+
 Experts are named by tables of pointers and inner sizes, so the shared expert goes through the
 kernels as one more chosen expert with input weight 1 and its gate as the output weight.  A step
 of few tokens runs pair by pair (token, chosen expert) and reads only the chosen experts'
@@ -26,17 +31,23 @@ from .spec import WeightSpec
 class RoutedExperts(FeedForward):
     graph_safe = True
 
+    WEIGHTS = ("sigmoid_on_input", "softmax_of_chosen")
+
     def __init__(self, prefix, width: int, n_experts: int, top: int, expert_inner: int, shared_inner: int | None = None,
-                 names: dict | None = None):
+                 names: dict | None = None, weights: str = "sigmoid_on_input", router_bias: bool = False,
+                 shared_gate: bool = True):
         super().__init__(prefix)
+        if weights not in self.WEIGHTS:
+            raise ValueError(f"{prefix}: unknown rule for the experts' weights '{weights}' (known: {', '.join(self.WEIGHTS)})")
+        self.weights_rule, self.router_bias, self.shared_gate = weights, bool(router_bias), bool(shared_gate)
         self.width, self.n_experts, self.top, self.inner = int(width), int(n_experts), int(top), int(expert_inner)
         self.shared_inner = int(shared_inner) if shared_inner else None
         if not 1 <= self.top <= self.n_experts:
             raise ValueError(f"{prefix}: every token takes between 1 and {self.n_experts} experts, got {self.top}")
         if self.inner <= 0:
             raise ValueError(f"{prefix}: the experts' inner size must be positive")
-        self.names = dict(router="router", expert="e{index}", shared="shared", shared_gate="shared.sg", gate="gate", up="up",
-                          down="down")
+        self.names = dict(router="router", router_bias="router.b", expert="e{index}", shared="shared", shared_gate="shared.sg",
+                          gate="gate", up="up", down="down")
         self.names.update(names or {})
         self.pairs = self.top + (1 if self.shared_inner else 0)
 
@@ -53,8 +64,10 @@ class RoutedExperts(FeedForward):
             specs += [WeightSpec(self.full_name(f"{name}.{n['gate']}"), (inner, self.width)),
                       WeightSpec(self.full_name(f"{name}.{n['up']}"), (inner, self.width)),
                       WeightSpec(self.full_name(f"{name}.{n['down']}"), (self.width, inner), init="residual_matrix")]
-        if self.shared_inner:
+        if self.shared_inner and self.shared_gate:
             specs.append(WeightSpec(self.full_name(n["shared_gate"]), (1, self.width)))
+        if self.router_bias:
+            specs.append(WeightSpec(self.full_name(n["router_bias"]), (self.n_experts,), role="vector", init="bias"))
         return specs
 
     def bind(self, tensors, runtime):
@@ -83,15 +96,17 @@ class RoutedExperts(FeedForward):
         self.max_inner = max(inner for _, inner in experts)
         # the loaded matrices are held in the stacked ones now
         self.weights = {name: tensor for name, tensor in self.weights.items()
-                        if name in (self.full_name(n["router"]), self.full_name(n["shared_gate"]))}
+                        if name in (self.full_name(n["router"]), self.full_name(n["shared_gate"]), self.full_name(n["router_bias"]))}
 
     def forward(self, ctx, x, hidden):
         k, n = ctx.kernels, x.shape[0]
         choice = ctx.buffer("expert_choice", (n * self.pairs,), torch.int32)
         in_weight = ctx.buffer("expert_in_weight", (n * self.pairs,), torch.float32)
         out_weight = ctx.buffer("expert_out_weight", (n * self.pairs,), torch.float32)
-        k.route(x, self.w(self.names["router"]), self.w(self.names["shared_gate"]) if self.shared_inner else None, self.top,
-                choice, in_weight, out_weight)
+        gated = self.shared_inner and self.shared_gate
+        k.route(x, self.w(self.names["router"]), self.w(self.names["shared_gate"]) if gated else None, self.top,
+                choice, in_weight, out_weight, bias=self.w(self.names["router_bias"]) if self.router_bias else None,
+                softmax_of_chosen=self.weights_rule == "softmax_of_chosen", shared_plain=bool(self.shared_inner) and not gated)
         if k.experts_at_once(n, x, self.up_matrix, self.down_matrix):
             gu = ctx.buffer("expert_gate_up", (n, 2 * self.total), ctx.act_dtype)
             k.linear(ctx, gu, x, self.up_matrix)

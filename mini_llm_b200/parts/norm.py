@@ -79,9 +79,16 @@ class GroupedRmsNorm(Norm):
         ctx.kernels.grouped_rms_norm(hidden, hidden, self.w(self.name), self.groups, self.eps)
         return hidden
 
-    def add_normed(self, ctx, hidden, y):
-        """hidden += norm(y): a sublayer's fp32 result is normed on its way onto the stream."""
+    def add_normed(self, ctx, hidden, y, rounded=None):
+        """hidden += norm(y): a sublayer's fp32 result is normed on its way onto the stream.  ``rounded``: the
+        stream's rows as they then are also go there, in that tensor's element type (the same pass where the
+        norm is over the whole row)."""
+        if rounded is not None and self.groups == 1:
+            ctx.kernels.add_normed_cast(hidden, y, self.w(self.name), self.eps, rounded)
+            return hidden
         ctx.kernels.grouped_rms_norm(hidden, y, self.w(self.name), self.groups, self.eps, add=True)
+        if rounded is not None:
+            ctx.kernels.add_normed_cast(hidden, act=rounded)
         return hidden
 
 

@@ -18,6 +18,9 @@ its own: ``S <- a_t S + k_t u_t^T``, read after the write as ``S^T q_t``.  With
     row i of S before the old state is read; the step's projection is a product of two thin
     matrices, and so is the output gate, which is ``sigmoid(W_g2 (W_g1 x))``.
 
+``gated_linear_recurrence`` (the real-gated linear recurrent unit of Griffin): the state is a vector, one number per
+    channel: ``S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t`` with ``a_t = exp(-decay_scale * r_t * softplus(lam))``; see the class.
+
 State per request (32-bit, in its slot): S [heads, dim, vdim] and the convolution's last
 ``taps - 1`` inputs.  Steps, decays, write gates, unit norms and the recurrence are 32-bit; the
 projections that feed gates and steps leave their product in 32-bit.
@@ -271,6 +274,85 @@ class StateSpaceDuality(Mixer):
         ctx.kernels.scaled_add(hidden, self.compute(ctx, x, cache), 1.0)
 
 
+class GatedLinearRecurrence(Mixer):
+    """A recurrent block with two branches of ``inner`` channels: ``y = gelu_tanh(W_y x + b_y)`` and
+    ``u = conv(W_x x + b_x)``, a causal convolution per channel with a bias and no activation (the last ``taps - 1``
+    inputs of a request are state).  The channels are cut into ``blocks`` equal parts; in part b,
+    ``r = sigmoid(A_r[b] u_b + b_r[b])`` and ``i = sigmoid(A_i[b] u_b + b_i[b])`` with square matrices.  Then per channel
+    ``a = exp(-decay_scale * r * softplus(lam))`` and ``S_t = a S_(t-1) + sqrt(1 - a^2) * i * u`` from S = 0 (no special
+    case for a first token); the output is ``W_o (S * y)``.  Both input products are one product over the stacked
+    matrices and both gates one product per part; gates, decays and the state are 32-bit."""
+
+    graph_safe = True
+
+    def __init__(self, prefix, width: int, inner: int, blocks: int, taps: int, decay_scale: float = 8.0, names: dict | None = None):
+        super().__init__(prefix)
+        self.width, self.inner, self.blocks, self.taps = int(width), int(inner), int(blocks), int(taps)
+        self.decay_scale = float(decay_scale)
+        if self.blocks <= 0 or self.inner <= 0 or self.inner % self.blocks != 0:
+            raise ValueError(f"{prefix}: {self.inner} channels do not split into {self.blocks} equal parts")
+        if self.taps < 1:
+            raise ValueError(f"{prefix}: a convolution has at least one tap")
+        self.part = self.inner // self.blocks
+        self.names = dict(y="y", x="x", bias=".b", taps="conv", taps_bias="conv.b", gate_r="ra", gate_i="ri", rate="lam", o="o")
+        self.names.update(names or {})
+
+    def weight_specs(self):
+        n, part = self.names, self.part
+        return [
+            WeightSpec(self.full_name(n["y"]), (self.inner, self.width)),
+            WeightSpec(self.full_name(n["y"] + n["bias"]), (self.inner,), role="vector", init="bias"),
+            WeightSpec(self.full_name(n["x"]), (self.inner, self.width)),
+            WeightSpec(self.full_name(n["x"] + n["bias"]), (self.inner,), role="vector", init="bias"),
+            WeightSpec(self.full_name(n["taps"]), (self.inner, self.taps), role="vector", init="matrix"),
+            WeightSpec(self.full_name(n["taps_bias"]), (self.inner,), role="vector", init="bias"),
+            WeightSpec(self.full_name(n["gate_r"]), (self.blocks, part, part)),
+            WeightSpec(self.full_name(n["gate_r"] + n["bias"]), (self.blocks, part), role="vector", init="bias"),
+            WeightSpec(self.full_name(n["gate_i"]), (self.blocks, part, part)),
+            WeightSpec(self.full_name(n["gate_i"] + n["bias"]), (self.blocks, part), role="vector", init="bias"),
+            WeightSpec(self.full_name(n["rate"]), (self.inner,), role="vector", init="shift"),
+            WeightSpec(self.full_name(n["o"]), (self.width, self.inner), init="residual_matrix"),
+        ]
+
+    def cache_need(self):
+        need = {"state": FixedState((self.inner,), "float32")}
+        if self.taps > 1:
+            need["taps"] = FixedState((self.taps - 1, self.inner), "float32")
+        return need
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        n = self.names
+        self.stacked = torch.cat([self.w(n["y"]), self.w(n["x"])]).contiguous()
+        self.stacked_bias = torch.cat([self.w(n["y"] + n["bias"]), self.w(n["x"] + n["bias"])]).contiguous()
+        # per part: the rows of its r gate, then those of its i gate
+        self.gate_matrices = torch.cat([self.w(n["gate_r"]), self.w(n["gate_i"])], dim=1).contiguous()
+        self.bias_r = self.w(n["gate_r"] + n["bias"]).reshape(-1).contiguous()
+        self.bias_i = self.w(n["gate_i"] + n["bias"]).reshape(-1).contiguous()
+        self._no_state = torch.zeros((1, 0, self.inner), dtype=torch.float32, device=self.stacked.device)
+
+    def compute(self, ctx, x, cache):
+        k, n, names, inner = ctx.kernels, x.shape[0], self.names, self.inner
+        both = ctx.buffer("unit_branches", (n, 2 * inner), ctx.act_dtype)
+        k.linear(ctx, both, x, self.stacked, self.stacked_bias)
+        held = cache.of("taps") if self.taps > 1 else None
+        u = ctx.buffer("unit_filtered", (n, inner), ctx.act_dtype)
+        k.causal_taps(ctx, u, both[:, inner:], self.w(names["taps"]), held.state if held is not None else self._no_state,
+                      held.writes if held is not None else False, identity=False, bias=self.w(names["taps_bias"]))
+        gates = ctx.buffer("unit_gates", (n, 2 * inner), torch.float32)
+        k.head_linear(ctx, gates, u, self.gate_matrices, self.blocks, self.part, 2 * self.part)
+        state = cache.of("state")
+        mixed = ctx.buffer("attn_out", (n, inner), ctx.act_dtype)
+        k.gated_recurrence(ctx, mixed, u, both[:, :inner], gates, self.bias_r, self.bias_i, self.w(names["rate"]),
+                           self.decay_scale, state.state, self.part, state.writes)
+        out = ctx.buffer("unit_out", (n, self.width), torch.float32)
+        k.linear(ctx, out, mixed, self.w(names["o"]))
+        return out
+
+    def forward(self, ctx, x, hidden, cache):
+        ctx.kernels.scaled_add(hidden, self.compute(ctx, x, cache), 1.0)
+
+
 class ParallelMixers(Mixer):
     """Several mixers side by side on one input: the stream gets ``sum_i scale_i * mixer_i(x)``.
     ``branches``: a tuple of (name, description of the mixer, scale); each mixer has ``compute`` and
@@ -311,8 +393,16 @@ class ParallelMixers(Mixer):
             mine = cache.sub(name) if isinstance(part.cache_need(), dict) else cache.of(name)
             ctx.kernels.scaled_add(hidden, part.compute(ctx, x, mine), scale)
 
+    def compute(self, ctx, x, cache):
+        """The weighted sum itself, in 32-bit, for arrangements that norm a mixer's output before the residual sum."""
+        out = ctx.buffer("parallel_out", tuple(x.shape), torch.float32)      # (every mixer maps the width onto itself)
+        out.zero_()
+        self.forward(ctx, x, out, cache)
+        return out
+
 
 register_part("gated_delta_memory", GatedDeltaMemory)
 register_part("channel_delta_memory", ChannelDeltaMemory)
 register_part("state_space_duality", StateSpaceDuality)
+register_part("gated_linear_recurrence", GatedLinearRecurrence)
 register_part("parallel_mixers", ParallelMixers)
