@@ -32,7 +32,7 @@ def _attention(sizes: dict, prefix: str, width: int, eps: float, norm: str, layo
     return PartSpec("normed_attention", prefix, {
         "width": width, "n_heads": sizes["heads"], "n_kv_heads": sizes["kv_heads"], "key_size": sizes["dim"],
         "value_size": sizes["vdim"], "score_scale": sizes["scale"], "eps": eps, "position": rotation, "norm": norm,
-        "values": values, "taps": sizes["conv"] or 1, "softcap": sizes["softcap"],
+        "values": values, "taps": sizes["conv"], "softcap": sizes["softcap"],
         "window": sizes["mask"]["size"] if sizes["mask"] else None, "sink": sink, "own_kv": sizes.get("kv_from") is None})
 
 

@@ -298,12 +298,12 @@ class NormedAttention(Mixer):
     graph_safe = True
 
     def __init__(self, prefix, width: int, n_heads: int, n_kv_heads: int, key_size: int, value_size: int, score_scale: float,
-                 eps: float, position, norm: str | None = "whole", values: str = "projected", taps: int = 1,
+                 eps: float, position, norm: str | None = "whole", values: str = "projected", taps: int | None = None,
                  softcap: float | None = None, window: int | None = None, sink: bool = False, own_kv: bool = True,
                  names: dict | None = None):
         super().__init__(prefix)
         self.width, self.n_heads, self.n_kv_heads = int(width), int(n_heads), int(n_kv_heads)
-        self.dim, self.vdim, self.taps = int(key_size), int(value_size), int(taps)
+        self.dim, self.vdim, self.taps = int(key_size), int(value_size), int(taps) if taps is not None else 0
         self.score_scale, self.eps = float(score_scale), float(eps)
         self.softcap = float(softcap) if softcap else 0.0
         self.window = int(window) if window else None
@@ -316,7 +316,7 @@ class NormedAttention(Mixer):
             raise ValueError(f"{prefix}: the values are 'projected' or the 'keys', got '{values}'")
         if values == "keys" and self.vdim != self.dim:
             raise ValueError(f"{prefix}: values that are the keys have the keys' size {self.dim}, not {self.vdim}")
-        if self.taps < 1:
+        if self.taps < 0:
             raise ValueError(f"{prefix}: a convolution has at least one tap")
         self.norm, self.values = norm, values
         self.position = build_part(position)
@@ -337,7 +337,7 @@ class NormedAttention(Mixer):
         specs = list(self.position.weight_specs())
         for key, rows in self.projections:
             specs.append(WeightSpec(self.full_name(n[key]), (rows, self.width)))
-            if self.taps > 1:
+            if self.taps >= 1:
                 specs.append(WeightSpec(self.full_name(n[key] + n["taps"]), (rows, self.taps), role="vector", init="matrix"))
             if self.norm is not None and key != "v":
                 specs.append(WeightSpec(self.full_name(n[key] + n["norm"]), (rows if self.norm == "whole" else self.dim,),
@@ -360,7 +360,8 @@ class NormedAttention(Mixer):
         self.position.bind({w.name: tensors[w.name] for w in self.position.weight_specs() if w.name in tensors}, runtime)
         keys = [key for key, _ in self.projections]
         self.stacked = torch.cat([self.w(n[key]) for key in keys]).contiguous()
-        self.stacked_taps = torch.cat([self.w(n[key] + n["taps"]) for key in keys]).contiguous() if self.taps > 1 else None
+        self.stacked_taps = torch.cat([self.w(n[key] + n["taps"]) for key in keys]).contiguous() if self.taps >= 1 else None
+        self._no_state = torch.zeros((1, 0, self.proj_width), dtype=torch.float32, device=self.stacked.device)
         self.q_gain = self.w(n["q"] + n["norm"]) if self.norm is not None else None
         self.k_gain = self.w(n["k"] + n["norm"]) if self.norm is not None and self.own_kv else None
 
@@ -373,10 +374,11 @@ class NormedAttention(Mixer):
         # projections, taps, norm and rotation in 32-bit: the queries and the cache are rounded once
         projected = ctx.buffer("qkv_32", (n, self.proj_width), torch.float32)
         k.linear(ctx, projected, x, self.stacked)
-        if self.taps > 1:
-            held = cache.of("taps")
+        if self.taps >= 1:
+            held = cache.of("taps") if self.taps > 1 else None
             filtered = ctx.buffer("qkv_32_filtered", (n, self.proj_width), torch.float32)
-            k.causal_taps(ctx, filtered, projected, self.stacked_taps, held.state, held.writes, identity=False)
+            k.causal_taps(ctx, filtered, projected, self.stacked_taps, held.state if held is not None else self._no_state,
+                          held.writes if held is not None else False, identity=False)
             projected = filtered
         q = ctx.buffer("q", (n, self.q_width), ctx.act_dtype)
         k_off = self.q_width

@@ -217,3 +217,31 @@ def forward(config, w, tokens, keep_layers=False):
     if cap:
         logits = cap * np.tanh(logits / cap)
     return (logits, kept) if keep_layers else logits
+
+
+def load_model(folder):
+    """(config dictionary, {name: float64 array}) of a model folder; its own small safetensors reader."""
+    import json
+    import os
+    import struct
+
+    with open(os.path.join(folder, "config.json")) as handle:
+        config = json.load(handle)
+    with open(os.path.join(folder, "model.safetensors"), "rb") as handle:
+        data = handle.read()
+    (length,) = struct.unpack("<Q", data[:8])
+    header = json.loads(data[8:8 + length])
+    body = data[8 + length:]
+    tensors = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        begin, end = info["data_offsets"]
+        if info["dtype"] == "F32":
+            values = np.frombuffer(body[begin:end], dtype="<f4").astype(np.float64)
+        elif info["dtype"] == "BF16":
+            values = (np.frombuffer(body[begin:end], dtype="<u2").astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+        else:
+            raise ValueError(f"{name}: element type {info['dtype']}")
+        tensors[name] = values.reshape(info["shape"])
+    return config, tensors
