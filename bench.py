@@ -64,12 +64,14 @@ def parse_args():
     parser.add_argument("--kernels", action="store_true",
                         help="time single kernels (matrix products at forced tile widths, prompt attention) back to "
                              "back in a replayed graph and print one line each: the tables of profiles/ come from this")
-    parser.add_argument("--compare", default=None, choices=("fuvolix", "sumozen", "lipulorn"),
+    parser.add_argument("--compare", default=None, choices=("fuvolix", "sumozen", "lipulorn", "deluvik"),
                         help="fuvolix: prefill and decode of Fuvolix stacks at sizes of real layers (random weights), beside "
                              "GPT-2 of equal width, depth and inner size, and their mixers' kernels alone; sumozen: Sumozen "
                              "stacks beside Fuvolix stacks of equal width, depth and inner size, and its kernels alone; "
                              "lipulorn: Lipulorn stacks beside Fuvolix stacks of equal width, depth and feed-forward weights, and "
-                             "its kernels alone beside the like kernels of Fuvolix and Sumozen; one line each")
+                             "its kernels alone beside the like kernels of Fuvolix and Sumozen; deluvik: Deluvik stacks beside "
+                             "Sumozen stacks of equal width, depth and experts, and its kernels alone beside Sumozen's like kernels; "
+                             "one line each")
     parser.add_argument("--tokens-out", default=None,
                         help="(--impl reference) write the greedy tokens of the fixed check workload to this file "
                              "and print nothing else")
@@ -1325,6 +1327,187 @@ def run_compare_lipulorn(args):
     return 0
 
 
+# Deluvik stacks beside Sumozen of equal width, depth and experts: layers in fours (attention with convolved
+# projections, attention whose values are its keys, a sliding-window attention beside the gated linear recurrence, and
+# attention with convolved queries over the first layer's keys and values), every layer with the routed feed-forward
+# that the Sumozen stack has (the first of every four a dense one of the same inner size).
+DELUVIK_SIZES = {
+    "small": {"width": 768, "layers": 12, "ff": 3072, "sumozen": "small",
+              "attention": {"heads": 12, "kv_heads": 4, "dim": 64, "vdim": 64}, "window": 512,
+              "unit": {"width": 768, "blocks": 12}, "moe": {"experts": 8, "top": 2, "ff": 768, "shared": 1536}},
+    "medium": {"width": 1024, "layers": 24, "ff": 4096, "sumozen": "medium",
+               "attention": {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 64}, "window": 512,
+               "unit": {"width": 1024, "blocks": 16}, "moe": {"experts": 8, "top": 2, "ff": 1024, "shared": 2048}},
+}
+
+
+def deluvik_config(size: dict, vocab: int) -> dict:
+    att, moe = size["attention"], size["moe"]
+    routed = {"kind": "moe", "router": {"experts": moe["experts"], "top": moe["top"]}, "expert": {"ff": moe["ff"]},
+              "shared": {"ff": moe["shared"]}}
+    rot = {"base": 10000.0, "dims": att["dim"]}
+    banded = dict(rot, scaling={"factor": 8.0, "low": 1.0, "high": 4.0, "original": 1024})
+    common = dict(att, scale=att["dim"] ** -0.5)
+
+    def four(first):
+        return [{"type": "attention_2", "mixer": dict(common, conv=4, rot=rot), "mlp": {"kind": "dense", "ff": size["ff"]}},
+                {"type": "attention", "mixer": dict(common, kv_heads=1, rot=banded, softcap=50.0), "mlp": routed},
+                {"type": "parallel", "mlp": routed, "mixer": {
+                    "left": dict(common, kv_heads=1, rot=dict(rot, dims=att["dim"] // 2), mask={"size": size["window"]}),
+                    "right": dict(size["unit"], conv=4), "left_scale": 1.0, "right_scale": 1.0}},
+                {"type": "attention_2", "mixer": dict(common, conv=4, rot=rot, kv_from=first), "mlp": routed}]
+    layers = []
+    while len(layers) < size["layers"]:
+        layers += four(len(layers))
+    return {"architecture": "Deluvik", "vocab": vocab, "width": size["width"], "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "layers": layers[:size["layers"]]}
+
+
+def deluvik_kernels(torch, size: dict, peak: dict):
+    """Deluvik's own kernels alone, replayed back to back on operands of their own: prompt portions (2 x 1,024 tokens)
+    and single tokens (8 requests at 1,023 cached tokens), each with the work it must do and the fraction of its
+    bound (32-bit FMA, nominal, where the sums are 32-bit by the design's rule; measured HBM copy bandwidth where
+    rows, the cache or the state are streamed)."""
+    from mini_llm_b200.kernels import ops
+    lines = []
+    page, fma_peak = 64, FP32_FMA_TFLOPS_NOMINAL
+    dev = lambda values: torch.tensor(values, dtype=torch.int32, device="cuda")
+
+    def add(kernel, us, flops=None, bytes_moved=None, **more):
+        line = {"kernel": kernel, "us": round(us, 2), **more}
+        if flops is not None:
+            line.update(tflops=round(flops / us / 1e6, 2), frac_fp32_fma_nominal=round(flops / us / 1e6 / fma_peak, 3))
+        if bytes_moved is not None:
+            line.update(gbs=round(bytes_moved / us / 1e3, 1), frac_hbm_measured=round(bytes_moved / us / 1e3 / peak["hbm_gbs"], 3))
+        lines.append(line)
+
+    att = size["attention"]
+    heads, kv_heads, dim, vdim, width = att["heads"], att["kv_heads"], att["dim"], att["vdim"], size["width"]
+    for name, lengths, new in (("prompts, 2 x 1024", [1024, 1024], [1024, 1024]), ("single tokens, 8 x 1024", [1024] * 8, [1] * 8)):
+        blocks = [-(-n // page) for n in lengths]
+        table = torch.zeros(len(lengths), max(blocks), dtype=torch.int32)
+        at = 0
+        for i, count in enumerate(blocks):
+            table[i, :count] = torch.arange(at, at + count, dtype=torch.int32)
+            at += count
+        table = table.cuda()
+        n = sum(new)
+        starts = [length - count for length, count in zip(lengths, new)]
+        positions = torch.cat([torch.arange(s, s + m) for s, m in zip(starts, new)]).int().cuda()
+        token_item = torch.cat([torch.full((m,), i) for i, m in enumerate(new)]).int().cuda()
+        k_pages = [torch.randn(sum(blocks) + 1, page, kv_heads, dim, device="cuda").bfloat16() for _ in range(4)]
+        v_pages = [torch.randn(sum(blocks) + 1, page, kv_heads, vdim, device="cuda").bfloat16() for _ in range(4)]
+        q = torch.randn(n, heads * dim, device="cuda").bfloat16()
+        out = torch.empty(n, heads * vdim, device="cuda", dtype=torch.bfloat16)
+        sink = torch.randn(heads, device="cuda")
+        window = size["window"]
+        if len(new) == 2:
+            pairs = sum(sum(range(s + 1, s + m + 1)) for s, m in zip(starts, new)) * heads         # (query row, key) pairs
+            us = replayed_us(torch, lambda i: ops.capped_attention(out, q, k_pages[i % 4], v_pages[i % 4], table, positions, token_item,
+                                                                   heads, kv_heads, dim, vdim, page, 0.125, 50.0, 0, tiled=True, sink=sink))
+            add(f"attention in tiles with a sink, {name}", us, flops=2.0 * pairs * (dim + vdim), heads=heads, kv_heads=kv_heads, dim=dim)
+            seen = sum(sum(min(p + 1, window) for p in range(s, s + m)) for s, m in zip(starts, new)) * heads
+            us = replayed_us(torch, lambda i: ops.capped_attention(out, q, k_pages[i % 4], v_pages[i % 4], table, positions, token_item,
+                                                                   heads, kv_heads, dim, vdim, page, 0.125, 0.0, window, tiled=True))
+            add(f"attention in tiles within a window of {window}, {name}", us, flops=2.0 * seen * (dim + vdim), heads=heads,
+                kv_heads=kv_heads, dim=dim)
+        else:
+            chunk, reach = 128, table.shape[1] * page
+            chunks = -(-reach // chunk)
+            scratch = (torch.empty(n * heads * chunks * dim, device="cuda"), torch.empty(n * heads * chunks * 2, device="cuda"),
+                       torch.zeros(n * heads, dtype=torch.int32, device="cuda"))
+            us = replayed_us(torch, lambda i: ops.split_attention(out, q, k_pages[i % 4], v_pages[i % 4], table, positions, token_item,
+                                                                  heads, kv_heads, dim, page, 0.125, 0, chunk, chunks, *scratch, cap=50.0,
+                                                                  sink=sink))
+            add(f"attention over split keys with a sink, {name}", us, bytes_moved=sum(lengths) * kv_heads * (dim + vdim) * 2.0,
+                heads=heads, kv_heads=kv_heads, dim=dim)
+        # norm, rotation and the cache store: reads the 32-bit projections, writes the queries and the pages
+        row = (heads + 2 * kv_heads) * dim
+        projected = [torch.randn(n, row, device="cuda") for _ in range(4)]
+        q_gain, k_gain = torch.ones(heads * dim, device="cuda"), torch.ones(kv_heads * dim, device="cuda")
+        inv_freq = torch.tensor([10000.0 ** (-2.0 * i / dim) for i in range(dim // 2)], dtype=torch.float64, device="cuda")
+        us = replayed_us(torch, lambda i: ops.norm_rotary_store(projected[i % 4], heads * dim, (heads + kv_heads) * dim, heads, kv_heads, dim,
+                                                                vdim, q, q_gain, k_gain, "whole", 1e-5, dim, "half", inv_freq, positions,
+                                                                token_item, table, page, k_pages[i % 4], v_pages[i % 4]))
+        add(f"query and key norm, rotation and cache store, {name}", us, bytes_moved=n * row * 6.0, heads=heads, kv_heads=kv_heads, dim=dim)
+        # the like kernel of the closest design: rotation and cache store (16-bit rows in place)
+        rows16 = [torch.randn(n, row, device="cuda").bfloat16() for _ in range(4)]
+        us = replayed_us(torch, lambda i: ops.rotary_store(rows16[i % 4], heads * dim, (heads + kv_heads) * dim, heads, kv_heads, dim, vdim, dim,
+                                                           inv_freq, 1.0, positions, token_item, table, page, k_pages[i % 4], v_pages[i % 4]))
+        add(f"(Sumozen) rotation and cache store, {name}", us, bytes_moved=n * ((heads + kv_heads) * dim * 4.0 + 2 * kv_heads * dim * 2.0 + kv_heads * dim * 2.0),
+            heads=heads, kv_heads=kv_heads, dim=dim)
+    # ---- the gated linear recurrence, the sum with the norm, the router ----
+    inner, parts = size["unit"]["width"], size["unit"]["blocks"]
+    for name, counts in (("prompts, 2 x 1024", [1024, 1024]), ("single tokens, 8", [1] * 8)):
+        n = sum(counts)
+        both = [torch.randn(n, 2 * inner, device="cuda").bfloat16() for _ in range(4)]
+        u = [torch.randn(n, inner, device="cuda").bfloat16() for _ in range(4)]
+        gates = [torch.randn(n, 2 * inner, device="cuda") for _ in range(4)]
+        states = [torch.zeros(len(counts), inner, device="cuda") for _ in range(4)]
+        out = torch.empty(n, inner, device="cuda", dtype=torch.bfloat16)
+        bias_r, bias_i, lam = torch.zeros(inner, device="cuda"), torch.zeros(inner, device="cuda"), torch.randn(inner, device="cuda")
+        slots, offs, cnts = dev(list(range(len(counts)))), dev([sum(counts[:i]) for i in range(len(counts))]), dev(counts)
+        us = replayed_us(torch, lambda i: ops.gated_recurrence(out, u[i % 4], both[i % 4][:, :inner], gates[i % 4], bias_r, bias_i, lam, 8.0,
+                                                               states[i % 4], slots, offs, cnts, inner // parts))
+        add(f"gated linear recurrence, {name}", us, bytes_moved=n * inner * (2 + 2 + 8 + 2.0) + 2.0 * len(counts) * inner * 4, inner=inner)
+        hidden = [torch.randn(n, width, device="cuda") for _ in range(4)]
+        y = [torch.randn(n, width, device="cuda") for _ in range(4)]
+        gain = torch.ones(width, device="cuda")
+        rounded = torch.empty(n, width, device="cuda", dtype=torch.bfloat16)
+        us = replayed_us(torch, lambda i: ops.add_normed_cast(hidden[i % 4], y[i % 4], gain, 1e-5, rounded))
+        add(f"residual sum of a normed result with the rounded rows, {name}", us, bytes_moved=n * width * (4 + 4 + 4 + 2.0), width=width)
+        normed = torch.empty(n, width, device="cuda", dtype=torch.bfloat16)
+        us = replayed_us(torch, lambda i: ops.grouped_rms_norm(normed, hidden[i % 4], gain, 1, 1e-5))
+        add(f"(Sumozen) norm of the stream, {name}", us, bytes_moved=n * width * (4 + 2.0), width=width)
+        moe = size["moe"]
+        x = torch.randn(n, width, device="cuda").bfloat16()
+        router = (torch.randn(moe["experts"], width, device="cuda") * 0.5).bfloat16()
+        router_bias = torch.randn(moe["experts"], device="cuda")
+        shared_gate = (torch.randn(1, width, device="cuda") * 0.1).bfloat16()
+        pairs = moe["top"] + 1
+        choice = torch.zeros(n * pairs, dtype=torch.int32, device="cuda")
+        in_weight, out_weight = torch.zeros(n * pairs, device="cuda"), torch.zeros(n * pairs, device="cuda")
+        us = replayed_us(torch, lambda i: ops.route(x, router, None, moe["top"], choice, in_weight, out_weight, bias=router_bias,
+                                                    softmax_of_chosen=True, shared_plain=True))
+        add(f"router with the softmax of the chosen logits, {name}", us, bytes_moved=n * width * 2.0 + moe["experts"] * width * 2.0)
+        us = replayed_us(torch, lambda i: ops.route(x, router, shared_gate, moe["top"], choice, in_weight, out_weight))
+        add(f"(Sumozen) router with sigmoid scores, {name}", us, bytes_moved=n * width * 2.0 + (moe["experts"] + 1) * width * 2.0)
+    return lines
+
+
+def run_compare_deluvik(args):
+    """Deluvik beside Sumozen of equal width, depth and experts: the prompt step of 2,048 tokens (2 x 1,024) and the
+    decode step of ``--batch`` requests at a context of 1,024, in bfloat16, through ``Engine.step``; then the kernels
+    alone, Deluvik's own and Sumozen's like ones.  One JSON line per measurement."""
+    import torch
+    from mini_llm_b200.config import config_from_dict
+    from mini_llm_b200.engine import Engine
+    from mini_llm_b200.weights import write_random_model
+    peak = peaks()
+    context, vocab = 1024, GPT2_SMALL["vocab_size"]
+    for name, size in DELUVIK_SIZES.items():
+        for design in ("deluvik", "sumozen"):
+            raw = deluvik_config(size, vocab) if design == "deluvik" else sumozen_config(SUMOZEN_SIZES[size["sumozen"]], vocab)
+            with tempfile.TemporaryDirectory() as folder:
+                write_random_model(config_from_dict(raw), 0, folder, recipe="gpt2", store_dtype="bfloat16")
+                engine = Engine(folder, dtype="bfloat16", max_requests=16, cache_tokens=16 * context, max_tokens_per_step=2048,
+                                **({"page_size": args.page_size} if args.page_size else {}))
+                prefill_ms = prefill_run(engine, 2, 1024, vocab)
+                decode_ms, launches, _ = decode_run(engine, args.batch, args.steps, args.warmup, context, vocab)
+                print(json.dumps({"design": design, "size": name, "width": size["width"], "layers": size["layers"], "inner": size["ff"],
+                                  "prefill_2048_tokens_ms": round(prefill_ms, 3), "prefill_tokens_per_s": round(2048 / prefill_ms * 1e3),
+                                  "decode_batch": args.batch, "decode_ms_per_step": round(decode_ms, 3),
+                                  "decode_tokens_per_s": round(args.batch / decode_ms * 1e3), "launches_per_decode_step": launches,
+                                  "weight_bytes": engine.model.weight_bytes, "step_kinds": engine.step_kinds}), flush=True)
+                del engine
+                torch.cuda.empty_cache()
+        for line in deluvik_kernels(torch, size, peak):
+            print(json.dumps(dict(line, design="deluvik", size=name)), flush=True)
+        for line in sumozen_kernels(torch, SUMOZEN_SIZES[size["sumozen"]], peak, recurrences=("mamba",), experts=False):
+            print(json.dumps(dict(line, design="sumozen", size=name)), flush=True)
+    return 0
+
+
 def run_compare(args):
     """Fuvolix beside GPT-2 of equal width, depth and inner size: the prompt step of 2,048 tokens
     (2 x 1,024) and the decode step of ``--batch`` requests at a context of 1,024, in bfloat16,
@@ -1371,6 +1554,8 @@ def main():
         return run_compare_sumozen(args)
     if args.compare == "lipulorn":
         return run_compare_lipulorn(args)
+    if args.compare == "deluvik":
+        return run_compare_deluvik(args)
     if args.compare:
         return run_compare(args)
     return run_ours(args)

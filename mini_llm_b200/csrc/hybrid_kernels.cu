@@ -932,6 +932,7 @@ template <> struct Vec16<bf16> {
     }
 };
 __device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<unsigned long long>(p) & 15ull) == 0; }
+static bool aligned_host(const void* p) { return (reinterpret_cast<unsigned long long>(p) & 15ull) == 0; }
 
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -1072,29 +1073,51 @@ expert_down_kernel(float* __restrict__ hidden, long ld_hidden, const T* __restri
 // gu: [T, 2 * total] = [gates of all experts | ups of all experts]; act: [T, total].  Columns
 // [e * inner, (e + 1) * inner) belong to routed expert e, columns from n_experts * inner on to the
 // shared expert (pair index `top` of every token, if there is one).
-template <typename T>
+// (VEC: a thread takes the 16 bytes of columns that lie side by side, all of one expert: inner sizes that are
+// multiples of a vector's elements.  The token's weights per expert lie in shared memory, 0 for an expert it
+// did not choose, whose columns are written as zeros without reading the products.)
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 expert_combine_kernel(T* __restrict__ act, long ld_act, const T* __restrict__ gu, long ld_gu, const int* __restrict__ choice,
                       const float* __restrict__ in_weight, const float* __restrict__ out_weight, int n_experts, int inner,
                       int total, int top, int pairs) {
     dependents_may_start();
     wait_for_earlier_kernels();
+    extern __shared__ float weights[];             // [n_experts + 1][2]: input weight, output weight
     const int t = blockIdx.x;
-    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < total; c += gridDim.y * blockDim.x) {
-        const int e = c < n_experts * inner ? c / inner : n_experts;
+    for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) {
         float s = 0.0f, o = 1.0f;
         if (e == n_experts) {
-            s = in_weight[(long)t * pairs + top], o = out_weight[(long)t * pairs + top];
+            if (pairs > top) s = in_weight[(long)t * pairs + top], o = out_weight[(long)t * pairs + top];
         } else {
             for (int k = 0; k < top; k++)
                 if (choice[(long)t * pairs + k] == e) s = in_weight[(long)t * pairs + k], o = out_weight[(long)t * pairs + k];
         }
-        float v = 0.0f;
-        if (s != 0.0f) {
-            const float g = s * to_f32(gu[(long)t * ld_gu + c]), u = s * to_f32(gu[(long)t * ld_gu + total + c]);
-            v = silu_f(g) * u * o;
+        weights[2 * e] = s, weights[2 * e + 1] = o;
+    }
+    __syncthreads();
+    constexpr int N = VEC ? Vec16<T>::N : 1;
+    const T* row = gu + (long)t * ld_gu;
+    T* dst = act + (long)t * ld_act;
+    for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * N; c < total; c += gridDim.y * blockDim.x * N) {
+        const int e = c < n_experts * inner ? c / inner : n_experts;
+        const float s = weights[2 * e], o = weights[2 * e + 1];
+        if (VEC) {
+            uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+            if (s != 0.0f) {
+                float g[N], u[N];
+                Vec16<T>::load(row + c, g);
+                Vec16<T>::load(row + total + c, u);
+                T* lanes = reinterpret_cast<T*>(&packed);
+#pragma unroll
+                for (int i = 0; i < N; i++) lanes[i] = from_f32<T>(silu_f(s * g[i]) * (s * u[i]) * o);
+            }
+            *reinterpret_cast<uint4*>(dst + c) = packed;
+        } else {
+            float v = 0.0f;
+            if (s != 0.0f) v = silu_f(s * to_f32(row[c])) * (s * to_f32(row[total + c])) * o;
+            dst[c] = from_f32<T>(v);
         }
-        act[(long)t * ld_act + c] = from_f32<T>(v);
     }
 }
 
@@ -1102,18 +1125,22 @@ extern "C" int mllm_hybrid_expert_combine(void* act, long ld_act, const void* gu
                                           const float* in_weight, const float* out_weight, int n_experts, int inner, int total,
                                           int top, int pairs, int n_tokens, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
+    if (dtype != DT_F32 && dtype != DT_BF16) return fail("expert_combine: unknown dtype");
     cudaStream_t s = (cudaStream_t)stream;
-    int y = (total + 255) / 256;
+    const int n = dtype == DT_F32 ? 4 : 8;
+    const bool vec = inner % n == 0 && total % n == 0 && ld_act % n == 0 && ld_gu % n == 0 && aligned_host(act) && aligned_host(gu);
+    const int per_block = 256 * (vec ? n : 1);
+    int y = (total + per_block - 1) / per_block;
     if (y > 64) y = 64;
     dim3 grid(n_tokens, y);
-    if (dtype == DT_F32)
-        launch_kernel(g_dependent_launch != 0, expert_combine_kernel<float>, grid, dim3(256), 0, s, (float*)act, ld_act,
-                      (const float*)gu, ld_gu, choice, in_weight, out_weight, n_experts, inner, total, top, pairs);
-    else if (dtype == DT_BF16)
-        launch_kernel(g_dependent_launch != 0, expert_combine_kernel<bf16>, grid, dim3(256), 0, s, (bf16*)act, ld_act,
-                      (const bf16*)gu, ld_gu, choice, in_weight, out_weight, n_experts, inner, total, top, pairs);
-    else
-        return fail("expert_combine: unknown dtype");
+    const size_t shared = sizeof(float) * 2 * ((size_t)n_experts + 1);
+    if (shared > 48 * 1024) return fail("expert_combine: too many experts for the table of weights");
+#define RUN(T, VEC)                                                                                                             \
+    launch_kernel(g_dependent_launch != 0, expert_combine_kernel<T, VEC>, grid, dim3(256), shared, s, (T*)act, ld_act, (const T*)gu, \
+                  ld_gu, choice, in_weight, out_weight, n_experts, inner, total, top, pairs)
+    if (dtype == DT_F32) { if (vec) RUN(float, true); else RUN(float, false); }
+    else { if (vec) RUN(bf16, true); else RUN(bf16, false); }
+#undef RUN
     return check_launch("expert_combine_kernel");
 }
 

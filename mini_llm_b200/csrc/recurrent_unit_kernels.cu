@@ -9,7 +9,7 @@
 //                      r_t and i_t the sigmoids of two gates; the output is S_t times gelu(y_t); state and
 //                      every gate in 32-bit
 //   add_normed_cast    hidden += norm(y) on the 32-bit residual stream, and the new rows rounded to the
-//                      activations' type in the same pass; to_activation: the rounding alone
+//                      activations' type in the same pass (without y: the rounding alone)
 //   softcap_rows       x <- cap * tanh(x / cap) on 32-bit rows (logits)
 // Every kernel that stores activations is templated on their element type (float: the true 32-bit path;
 // bfloat16: the serving path) and is launched as a programmatic dependent of the kernel before it.
@@ -149,16 +149,20 @@ extern "C" int mllm_unit_norm_rotary_store(const float* qkv, long ld, int k_off,
 // with S from the request's slot of `state` (32-bit; zero for a new request, also for its first token).
 // `gates` holds, for block b of `block_width` channels, 2 * block_width columns: the r gates of the block's
 // channels, then their i gates (the result of one product per block over both gate matrices).
-// A block of threads takes 32 channels of one entry; its `segments` rows of threads take consecutive
-// runs of the entry's tokens.  With more than one segment every thread first folds its run into
-// (A, B), S_out = A S_in + B, the runs' (A, B) are chained through shared memory, and the thread walks
-// its run again from its true S_in.  1 - a^2 is taken as -expm1(2 log a), which keeps its digits where a
-// is close to 1.
+// A block of threads takes UNIT_CHANNELS channels of one entry; its `segments` rows of threads take consecutive runs
+// of UNIT_RUN tokens, so the block walks the entry's tokens segments * UNIT_RUN at a time.  Every thread
+// computes the gates, a_t and the written value of its run's tokens once (the loads and exponentials of
+// different tokens do not wait on one another) and keeps, per token, the product P_t of the run's decays up
+// to it and the state s_t the run alone would have built from zero; the runs' (P, s) at their ends are
+// chained through shared memory, and then S_t = P_t S_in + s_t.  1 - a^2 is taken as -expm1(2 log a), which
+// keeps its digits where a is close to 1.
 // ---------------------------------------------------------------------------
-constexpr int UNIT_CHANNELS = 32;
+constexpr int UNIT_MAX_SEGMENTS = 32;
 
-template <typename T>
-__global__ void __launch_bounds__(1024)
+// (UNIT_RUN tokens a run and UNIT_CHANNELS channels a block: 16 and 16 for steps with prompt portions; 1 and 32 for
+// steps of single tokens, where a thread has one token's work and nothing to chain)
+template <typename T, int UNIT_RUN, int UNIT_CHANNELS>
+__global__ void __launch_bounds__(UNIT_CHANNELS * (UNIT_RUN > 1 ? UNIT_MAX_SEGMENTS : 1))
 gated_recurrence_kernel(T* __restrict__ out, long ld_out, const T* __restrict__ u, long ld_u, const T* __restrict__ y, long ld_y,
                         const float* __restrict__ gates, long ld_g, const float* __restrict__ bias_r,
                         const float* __restrict__ bias_i, const float* __restrict__ lam, float decay_scale,
@@ -167,57 +171,68 @@ gated_recurrence_kernel(T* __restrict__ out, long ld_out, const T* __restrict__ 
                         int writes) {
     dependents_may_start();
     wait_for_earlier_kernels();
-    __shared__ float fold_a[32][UNIT_CHANNELS], fold_b[32][UNIT_CHANNELS];
-    const int c = blockIdx.x * UNIT_CHANNELS + threadIdx.x, seg = threadIdx.y, segments = blockDim.y;
+    __shared__ float fold_p[UNIT_MAX_SEGMENTS][UNIT_CHANNELS], fold_s[UNIT_MAX_SEGMENTS][UNIT_CHANNELS];
+    __shared__ float carried[UNIT_CHANNELS];
+    const int lane_c = threadIdx.x, seg = threadIdx.y, segments = blockDim.y;
+    const int c = blockIdx.x * UNIT_CHANNELS + lane_c;
     const int item = blockIdx.y;
     const int count = item_count[item];
     const long first = item_offset[item];
     const bool live = c < inner;
-    const int per = (count + segments - 1) / segments;
-    const int t0 = min(seg * per, count), t1 = min(t0 + per, count);
-    float rate = 0.0f, br = 0.0f, bi = 0.0f;
-    long r_col = 0, i_col = 0;
-    if (live) {
-        rate = -decay_scale * softplus_f(lam[c]);
-        br = bias_r[c], bi = bias_i[c];
-        r_col = (long)(c / block_width) * 2 * block_width + c % block_width;
-        i_col = r_col + block_width;
-    }
-    float s_in = 0.0f;
-    float* cell = state + (long)item_slot[item] * ld_state + c;
-    if (segments > 1) {
-        float fa = 1.0f, fb = 0.0f;
-        if (live)
-            for (int t = t0; t < t1; t++) {
-                const float* g = gates + (first + t) * ld_g;
-                const float log_a = rate * sigmoid_f(g[r_col] + br);
-                const float a = expf(log_a);
-                const float b = sqrtf(-expm1f(2.0f * log_a)) * sigmoid_f(g[i_col] + bi) * to_f32(u[(first + t) * ld_u + c]);
-                fa *= a;
-                fb = fmaf(a, fb, b);
-            }
-        fold_a[seg][threadIdx.x] = fa;
-        fold_b[seg][threadIdx.x] = fb;
-        __syncthreads();
-        if (live) {
-            s_in = *cell;
-            for (int k = 0; k < seg; k++) s_in = fmaf(fold_a[k][threadIdx.x], s_in, fold_b[k][threadIdx.x]);
+    const int cc = live ? c : 0;                       // (a thread past the last channel computes channel 0 and stores nothing)
+    const float rate = -decay_scale * softplus_f(lam[cc]);
+    const float br = bias_r[cc], bi = bias_i[cc];
+    const long r_col = (long)(cc / block_width) * 2 * block_width + cc % block_width;
+    const long i_col = r_col + block_width;
+    float* cell = state + (long)item_slot[item] * ld_state + cc;
+    if (seg == 0) carried[lane_c] = *cell;
+    const int stride = segments * UNIT_RUN;
+    for (int base = 0; base < count; base += stride) {
+        const int t0 = base + seg * UNIT_RUN;
+        float p[UNIT_RUN], s[UNIT_RUN];
+        float run_p = 1.0f, run_s = 0.0f;
+        // every load of the run is asked for before the first is used (a token past the entry's end reads its last one)
+        float gate_r[UNIT_RUN], gate_i[UNIT_RUN], in[UNIT_RUN], side[UNIT_RUN];
+#pragma unroll
+        for (int k = 0; k < UNIT_RUN; k++) {
+            const long row = first + min(t0 + k, count - 1);
+            gate_r[k] = gates[row * ld_g + r_col];
+            gate_i[k] = gates[row * ld_g + i_col];
+            in[k] = to_f32(u[row * ld_u + cc]);
+            side[k] = to_f32(y[row * ld_y + cc]);
         }
-    } else if (live) {
-        s_in = *cell;
+#pragma unroll
+        for (int k = 0; k < UNIT_RUN; k++) {
+            const float log_a = rate * sigmoid_f(gate_r[k] + br);
+            float a = expf(log_a);
+            float b = sqrtf(-expm1f(2.0f * log_a)) * sigmoid_f(gate_i[k] + bi) * in[k];
+            if (t0 + k >= count) a = 1.0f, b = 0.0f;
+            run_p *= a;
+            run_s = fmaf(a, run_s, b);
+            p[k] = run_p, s[k] = run_s;
+        }
+        float s_in;
+        if (segments > 1) {
+            fold_p[seg][lane_c] = run_p;
+            fold_s[seg][lane_c] = run_s;
+            __syncthreads();                             // the folds are written; `carried` holds the state before `base`
+            s_in = carried[lane_c];
+            for (int k = 0; k < seg; k++) s_in = fmaf(fold_p[k][lane_c], s_in, fold_s[k][lane_c]);
+        } else {
+            s_in = carried[lane_c];
+        }
+#pragma unroll
+        for (int k = 0; k < UNIT_RUN; k++) {
+            const int t = t0 + k;
+            if (t < count && live)
+                out[(first + t) * ld_out + c] = from_f32<T>(fmaf(p[k], s_in, s[k]) * gelu_tanh_f(side[k]));
+        }
+        if (segments > 1) __syncthreads();               // every thread has read `carried` and the folds
+        // the last row of threads ends on the last token of this stretch (an empty run hands its S_in on)
+        if (seg == segments - 1) carried[lane_c] = fmaf(run_p, s_in, run_s);
+        if (segments > 1 && base + stride < count) __syncthreads();
     }
-    if (!live) return;
-    float s = s_in;
-    for (int t = t0; t < t1; t++) {
-        const float* g = gates + (first + t) * ld_g;
-        const float log_a = rate * sigmoid_f(g[r_col] + br);
-        const float a = expf(log_a);
-        const float b = sqrtf(-expm1f(2.0f * log_a)) * sigmoid_f(g[i_col] + bi) * to_f32(u[(first + t) * ld_u + c]);
-        s = fmaf(a, s, b);
-        out[(first + t) * ld_out + c] = from_f32<T>(s * gelu_tanh_f(to_f32(y[(first + t) * ld_y + c])));
-    }
-    // the last row of threads ends on the entry's last token (an empty run hands its S_in on)
-    if (writes && seg == segments - 1) *cell = s;
+    if (writes && live && seg == segments - 1) *cell = carried[lane_c];
 }
 
 extern "C" int mllm_unit_gated_recurrence(void* out, long ld_out, const void* u, long ld_u, const void* y, long ld_y,
@@ -229,52 +244,84 @@ extern "C" int mllm_unit_gated_recurrence(void* out, long ld_out, const void* u,
     if (inner <= 0 || block_width <= 0 || inner % block_width != 0) return fail("gated_recurrence: the channels do not split into blocks");
     if (n_items > 65535) return fail("gated_recurrence: too many entries for one launch");
     cudaStream_t s = (cudaStream_t)stream;
-    // rows of threads: one for steps of single tokens; else about 16 tokens a run at the step's mean portion
+    // rows of threads: one for steps of single tokens; else as many runs as the step's mean portion has, up to 32
+    const bool single = n_tokens == n_items;
+    constexpr int RUN = 16, CHANNELS = 16, SINGLE_CHANNELS = 32;
     int segments = 1;
     const int mean = n_tokens / n_items;
-    while (segments < 32 && segments * 16 < mean) segments *= 2;
-    dim3 grid((inner + UNIT_CHANNELS - 1) / UNIT_CHANNELS, n_items), block(UNIT_CHANNELS, segments);
-    if (dtype == DT_F32)
-        launch_kernel(g_dependent_launch != 0, gated_recurrence_kernel<float>, grid, block, 0, s, (float*)out, ld_out, (const float*)u,
-                      ld_u, (const float*)y, ld_y, gates, ld_g, bias_r, bias_i, lam, decay_scale, state, ld_state, item_slot,
-                      item_offset, item_count, inner, block_width, writes);
-    else if (dtype == DT_BF16)
-        launch_kernel(g_dependent_launch != 0, gated_recurrence_kernel<bf16>, grid, block, 0, s, (bf16*)out, ld_out, (const bf16*)u,
-                      ld_u, (const bf16*)y, ld_y, gates, ld_g, bias_r, bias_i, lam, decay_scale, state, ld_state, item_slot,
-                      item_offset, item_count, inner, block_width, writes);
-    else
-        return fail("gated_recurrence: unknown dtype");
+    while (!single && segments < UNIT_MAX_SEGMENTS && segments * RUN < mean) segments *= 2;
+    const int channels = single ? SINGLE_CHANNELS : CHANNELS;
+    dim3 grid((inner + channels - 1) / channels, n_items), block(channels, segments);
+#define RUN_AS(T, R, C)                                                                                                           \
+    launch_kernel(g_dependent_launch != 0, gated_recurrence_kernel<T, R, C>, grid, block, 0, s, (T*)out, ld_out, (const T*)u, ld_u, \
+                  (const T*)y, ld_y, gates, ld_g, bias_r, bias_i, lam, decay_scale, state, ld_state, item_slot, item_offset,       \
+                  item_count, inner, block_width, writes)
+    if (dtype == DT_F32) { if (single) RUN_AS(float, 1, SINGLE_CHANNELS); else RUN_AS(float, RUN, CHANNELS); }
+    else if (dtype == DT_BF16) { if (single) RUN_AS(bf16, 1, SINGLE_CHANNELS); else RUN_AS(bf16, RUN, CHANNELS); }
+    else return fail("gated_recurrence: unknown dtype");
+#undef RUN_AS
     return check_launch("gated_recurrence_kernel");
 }
 
 // ---------------------------------------------------------------------------
 // hidden[t] += y[t] / sqrt(mean(y[t]^2) + eps) * gain, on the 32-bit residual stream (y == nullptr: nothing
 // is added); the row as it then is also goes, rounded, to `act` (may be null): what the next sublayer
-// reads.  A warp per row.
+// reads.  A block per row.
 // ---------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 add_normed_cast_kernel(float* __restrict__ hidden, const float* __restrict__ y, const float* __restrict__ gain, float eps,
-                       T* __restrict__ act, int width, int n_rows) {
+                       T* __restrict__ act, int width) {
     dependents_may_start();
     wait_for_earlier_kernels();
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (row >= n_rows) return;
-    float* h = hidden + (long)row * width;
-    float inv = 0.0f;
-    if (y != nullptr) {
-        const float* v = y + (long)row * width;
-        float sq = 0.0f;
-        for (int c = lane; c < width; c += 32) sq = fmaf(v[c], v[c], sq);
-        inv = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+    __shared__ float scratch[33];
+    const long row = blockIdx.x;
+    float* h = hidden + row * width;
+    const float* v = y != nullptr ? y + row * width : nullptr;
+    T* a = act != nullptr ? act + row * width : nullptr;
+    if (VEC) {
+        // 16-byte vectors; a thread's first vector of y stays in registers between the two passes
+        const int n = width / 4;
+        float4 kept = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float inv = 0.0f;
+        if (v != nullptr) {
+            float sq = 0.0f;
+            for (int i = threadIdx.x; i < n; i += blockDim.x) {
+                const float4 x = reinterpret_cast<const float4*>(v)[i];
+                if (i == (int)threadIdx.x) kept = x;
+                sq = fmaf(x.x, x.x, fmaf(x.y, x.y, fmaf(x.z, x.z, fmaf(x.w, x.w, sq))));
+            }
+            inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
+        }
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            float4 sum = reinterpret_cast<const float4*>(h)[i];
+            if (v != nullptr) {
+                const float4 x = i == (int)threadIdx.x ? kept : reinterpret_cast<const float4*>(v)[i];
+                const float4 g = reinterpret_cast<const float4*>(gain)[i];
+                sum.x = fmaf(x.x * inv, g.x, sum.x), sum.y = fmaf(x.y * inv, g.y, sum.y);
+                sum.z = fmaf(x.z * inv, g.z, sum.z), sum.w = fmaf(x.w * inv, g.w, sum.w);
+                reinterpret_cast<float4*>(h)[i] = sum;
+            }
+            if (a != nullptr) {
+                a[4 * i] = from_f32<T>(sum.x), a[4 * i + 1] = from_f32<T>(sum.y);
+                a[4 * i + 2] = from_f32<T>(sum.z), a[4 * i + 3] = from_f32<T>(sum.w);
+            }
+        }
+        return;
     }
-    for (int c = lane; c < width; c += 32) {
+    float inv = 0.0f;
+    if (v != nullptr) {
+        float sq = 0.0f;
+        for (int c = threadIdx.x; c < width; c += blockDim.x) sq = fmaf(v[c], v[c], sq);
+        inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
+    }
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float sum = h[c];
-        if (y != nullptr) {
-            sum += y[(long)row * width + c] * inv * gain[c];
+        if (v != nullptr) {
+            sum = fmaf(v[c] * inv, gain[c], sum);
             h[c] = sum;
         }
-        if (act != nullptr) act[(long)row * width + c] = from_f32<T>(sum);
+        if (a != nullptr) a[c] = from_f32<T>(sum);
     }
 }
 
@@ -284,15 +331,15 @@ extern "C" int mllm_unit_add_normed_cast(float* hidden, const float* y, const fl
     if (width <= 0) return fail("add_normed_cast: the width must be positive");
     if (y != nullptr && gain == nullptr) return fail("add_normed_cast: a norm needs its gain");
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid((n_rows + 7) / 8);
-    if (dtype == DT_F32)
-        launch_kernel(g_dependent_launch != 0, add_normed_cast_kernel<float>, grid, dim3(256), 0, s, hidden, y, gain, eps, (float*)act,
-                      width, n_rows);
-    else if (dtype == DT_BF16)
-        launch_kernel(g_dependent_launch != 0, add_normed_cast_kernel<bf16>, grid, dim3(256), 0, s, hidden, y, gain, eps, (bf16*)act,
-                      width, n_rows);
-    else
-        return fail("add_normed_cast: unknown dtype");
+    const bool vec = width % 4 == 0 && (((unsigned long long)hidden | (unsigned long long)y | (unsigned long long)gain) & 15ull) == 0;
+    const int threads = width >= 1024 ? 256 : 128;
+#define RUN(T, VEC)                                                                                                       \
+    launch_kernel(g_dependent_launch != 0, add_normed_cast_kernel<T, VEC>, dim3(n_rows), dim3(threads), 0, s, hidden, y, gain, eps, \
+                  (T*)act, width)
+    if (dtype == DT_F32) { if (vec) RUN(float, true); else RUN(float, false); }
+    else if (dtype == DT_BF16) { if (vec) RUN(bf16, true); else RUN(bf16, false); }
+    else return fail("add_normed_cast: unknown dtype");
+#undef RUN
     return check_launch("add_normed_cast_kernel");
 }
 
