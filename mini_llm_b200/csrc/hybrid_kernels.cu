@@ -900,7 +900,8 @@ extern "C" int mllm_hybrid_linear_recurrence(const RecurrenceParams* params, int
 //                chosen ones' OUTPUTS are weighed by the softmax over the chosen logits only, and
 //                their inputs by 1
 //   expert_up    act[pair, f] = silu(W_gate[e] x') * (W_up[e] x') with x' = weight * x
-//   expert_down  hidden[t] += sum over the token's pairs of out_weight * W_down[e] act[pair]
+//   expert_down  hidden[t] += sum over the token's pairs of out_weight * W_down[e] act[pair] (or, with `assign`,
+//                hidden[t] = that sum)
 // Experts are named by a table of pointers (gate, up, down) and inner sizes, so that experts of
 // different sizes (the shared one) go through the same kernels; the down matrices are column
 // ranges of one matrix [width, all inner sizes], so their rows lie ld_down apart.
@@ -1039,7 +1040,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 expert_down_kernel(float* __restrict__ hidden, long ld_hidden, const T* __restrict__ act, long ld_act,
                    const int* __restrict__ choice, const float* __restrict__ out_weight, const long long* __restrict__ down_of,
-                   const int* __restrict__ inner_of, long ld_down, int width, int pairs) {
+                   const int* __restrict__ inner_of, long ld_down, int width, int pairs, int assign) {
     dependents_may_start();
     wait_for_earlier_kernels();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1066,7 +1067,7 @@ expert_down_kernel(float* __restrict__ hidden, long ld_hidden, const T* __restri
             }
             total = fmaf(out_weight[pair], warp_sum(z), total);
         }
-        if (lane == 0) hidden[(long)t * ld_hidden + c] += total;
+        if (lane == 0) hidden[(long)t * ld_hidden + c] = assign ? total : hidden[(long)t * ld_hidden + c] + total;
     }
 }
 
@@ -1171,7 +1172,7 @@ extern "C" int mllm_hybrid_experts(float* hidden, long ld_hidden, void* act, lon
                                    const int* choice, const float* in_weight, const float* out_weight,
                                    const long long* gate_of, const long long* up_of, const long long* down_of,
                                    const int* inner_of, long ld_down, int max_inner, int width, int pairs, int n_tokens,
-                                   int dtype, void* stream) {
+                                   int assign, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t shared = sizeof(float) * (size_t)width;
@@ -1185,12 +1186,12 @@ extern "C" int mllm_hybrid_experts(float* hidden, long ld_hidden, void* act, lon
         launch_kernel(g_dependent_launch != 0, expert_up_kernel<float>, up_grid, dim3(256), shared, s, (float*)act, ld_act,
                       (const float*)x, ld_x, choice, in_weight, gate_of, up_of, inner_of, width, pairs);
         launch_kernel(g_dependent_launch != 0, expert_down_kernel<float>, down_grid, dim3(256), 0, s, hidden, ld_hidden,
-                      (const float*)act, ld_act, choice, out_weight, down_of, inner_of, ld_down, width, pairs);
+                      (const float*)act, ld_act, choice, out_weight, down_of, inner_of, ld_down, width, pairs, assign);
     } else if (dtype == DT_BF16) {
         launch_kernel(g_dependent_launch != 0, expert_up_kernel<bf16>, up_grid, dim3(256), shared, s, (bf16*)act, ld_act,
                       (const bf16*)x, ld_x, choice, in_weight, gate_of, up_of, inner_of, width, pairs);
         launch_kernel(g_dependent_launch != 0, expert_down_kernel<bf16>, down_grid, dim3(256), 0, s, hidden, ld_hidden,
-                      (const bf16*)act, ld_act, choice, out_weight, down_of, inner_of, ld_down, width, pairs);
+                      (const bf16*)act, ld_act, choice, out_weight, down_of, inner_of, ld_down, width, pairs, assign);
     } else {
         return fail("experts: unknown dtype");
     }
@@ -1198,23 +1199,23 @@ extern "C" int mllm_hybrid_experts(float* hidden, long ld_hidden, void* act, lon
 }
 
 // ---------------------------------------------------------------------------
-// x[r, c] += a * u[r, c] + b * v[r, c]  (32-bit; v may be null)
+// x[r, c] += a * u[r, c] + b * v[r, c]  (32-bit; v may be null; with `assign` x is set to the sum instead)
 // ---------------------------------------------------------------------------
 __global__ void scaled_add_kernel(float* __restrict__ x, const float* __restrict__ u, float a, const float* __restrict__ v,
-                                  float b, long n) {
+                                  float b, long n, int assign) {
     dependents_may_start();
     wait_for_earlier_kernels();
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
         float sum = a * u[i];
         if (v != nullptr) sum = fmaf(b, v[i], sum);
-        x[i] += sum;
+        x[i] = assign ? sum : x[i] + sum;
     }
 }
 
-extern "C" int mllm_hybrid_scaled_add(float* x, const float* u, float a, const float* v, float b, long n, void* stream) {
+extern "C" int mllm_hybrid_scaled_add(float* x, const float* u, float a, const float* v, float b, long n, int assign, void* stream) {
     if (n <= 0) return 0;
     long blocks = (n + 255) / 256;
     if (blocks > 4096) blocks = 4096;
-    launch_kernel(g_dependent_launch != 0, scaled_add_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, x, u, a, v, b, n);
+    launch_kernel(g_dependent_launch != 0, scaled_add_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, x, u, a, v, b, n, assign);
     return check_launch("scaled_add_kernel");
 }

@@ -163,10 +163,10 @@ class Kernels:
         return ops.route(x, router, shared_gate, top, choice, in_weight, out_weight, bias, softmax_of_chosen, shared_plain)
 
     def experts(self, hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_of, inner_of, max_inner, pairs,
-                ld_down=None):
+                ld_down=None, assign=False):
         self.launches += 2
         return ops.experts(hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_of, inner_of, max_inner, pairs,
-                           ld_down)
+                           ld_down, assign)
 
     EXPERTS_AT_ONCE_TOKENS = 32    # from here on a step's tokens go through all experts as two products
 
@@ -203,9 +203,9 @@ class Kernels:
         self.launches += 1
         return ops.softcap(x, cap)
 
-    def scaled_add(self, x, u, a, v=None, b=0.0):
+    def scaled_add(self, x, u, a, v=None, b=0.0, assign=False):
         self.launches += 1
-        return ops.scaled_add(x, u, a, v, b)
+        return ops.scaled_add(x, u, a, v, b, assign)
 
     def latent_prepare(self, ctx, cache, q_eff, down, q, gain, inv_freq, rank, rot, rot_dims, heads, dim, eps,
                        layout="interleaved"):

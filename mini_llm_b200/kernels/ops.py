@@ -1327,7 +1327,7 @@ def linear_recurrence(out, q, k, v, gate_a, gate_b, log_rate, step_bias, state, 
 
 
 _route = Function("hybrid", "mllm_hybrid_route", [P, L, P, P, P, I, I, I, I, I, P, P, P, I, I, P])
-_experts = Function("hybrid", "mllm_hybrid_experts", [P, L, P, L, P, L, P, P, P, P, P, P, P, L, I, I, I, I, I, P])
+_experts = Function("hybrid", "mllm_hybrid_experts", [P, L, P, L, P, L, P, P, P, P, P, P, P, L, I, I, I, I, I, I, P])
 _expert_combine = Function("hybrid", "mllm_hybrid_expert_combine", [P, L, P, L, P, P, P, I, I, I, I, I, I, I, P])
 
 
@@ -1360,12 +1360,14 @@ def route(x, router, shared_gate, top, choice, in_weight, out_weight, bias=None,
            out_weight.data_ptr(), n, dtype_code(x.dtype), _stream())
 
 
-def experts(hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_of, inner_of, max_inner, pairs, ld_down=None):
+def experts(hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_of, inner_of, max_inner, pairs, ld_down=None,
+            assign=False):
     """hidden[t] += sum over the token's ``pairs`` of out_weight * W_down[e] (silu(W_gate[e] x') * (W_up[e] x')),
     x' = in_weight * x[t] rounded to the activations' type; expert e's matrices are named by the
     int64 pointer tables ``gate_of``, ``up_of``, ``down_of`` and its inner size by ``inner_of`` (int32);
     the rows of every down matrix lie ``ld_down`` elements apart (None: ``max_inner``, for experts of
-    one size that are stored each by itself).  ``act`` [T * pairs, max_inner] is scratch."""
+    one size that are stored each by itself).  ``act`` [T * pairs, max_inner] is scratch.  ``assign``: ``hidden`` is set
+    to the sum instead of added to."""
     _check(hidden, "experts.hidden", torch.float32, 2)
     _check(x, "experts.x", None, 2)
     _check(act, "experts.act", x.dtype, 2)
@@ -1378,7 +1380,7 @@ def experts(hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_
     _experts(hidden.data_ptr(), hidden.stride(0), act.data_ptr(), act.stride(0), x.data_ptr(), x.stride(0), choice.data_ptr(),
              in_weight.data_ptr(), out_weight.data_ptr(), gate_of.data_ptr(), up_of.data_ptr(), down_of.data_ptr(),
              inner_of.data_ptr(), int(ld_down if ld_down is not None else max_inner), int(max_inner), width, int(pairs), n,
-             dtype_code(x.dtype), _stream())
+             int(bool(assign)), dtype_code(x.dtype), _stream())
     return hidden
 
 
@@ -1397,11 +1399,11 @@ def expert_combine(act, gu, choice, in_weight, out_weight, n_experts, inner, top
     return act
 
 
-_scaled_add = Function("hybrid", "mllm_hybrid_scaled_add", [P, P, F, P, F, L, P])
+_scaled_add = Function("hybrid", "mllm_hybrid_scaled_add", [P, P, F, P, F, L, I, P])
 
 
-def scaled_add(x, u, a, v=None, b=0.0):
-    """x += a * u + b * v (fp32, contiguous, equal shapes; ``v`` may be None)."""
+def scaled_add(x, u, a, v=None, b=0.0, assign=False):
+    """x += a * u + b * v (fp32, contiguous, equal shapes; ``v`` may be None); ``assign``: x = a * u + b * v."""
     _check(x, "scaled_add.x", torch.float32)
     _check(u, "scaled_add.u", torch.float32)
     if not x.is_contiguous() or not u.is_contiguous() or u.shape != x.shape:
@@ -1410,7 +1412,7 @@ def scaled_add(x, u, a, v=None, b=0.0):
         _check(v, "scaled_add.v", torch.float32)
         if not v.is_contiguous() or v.shape != x.shape:
             raise KernelError("scaled_add: v must be contiguous and of x's shape")
-    _scaled_add(x.data_ptr(), u.data_ptr(), float(a), _ptr(v), float(b), x.numel(), _stream())
+    _scaled_add(x.data_ptr(), u.data_ptr(), float(a), _ptr(v), float(b), x.numel(), int(bool(assign)), _stream())
     return x
 
 

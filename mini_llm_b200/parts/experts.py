@@ -98,7 +98,8 @@ class RoutedExperts(FeedForward):
         self.weights = {name: tensor for name, tensor in self.weights.items()
                         if name in (self.full_name(n["router"]), self.full_name(n["shared_gate"]), self.full_name(n["router_bias"]))}
 
-    def forward(self, ctx, x, hidden):
+    def forward(self, ctx, x, hidden, assign=False):
+        """``assign``: ``hidden`` becomes the experts' sum instead of growing by it."""
         k, n = ctx.kernels, x.shape[0]
         choice = ctx.buffer("expert_choice", (n * self.pairs,), torch.int32)
         in_weight = ctx.buffer("expert_in_weight", (n * self.pairs,), torch.float32)
@@ -112,16 +113,15 @@ class RoutedExperts(FeedForward):
             k.linear(ctx, gu, x, self.up_matrix)
             act = ctx.buffer("expert_act_all", (n, self.total), ctx.act_dtype)
             k.expert_combine(act, gu, choice, in_weight, out_weight, self.n_experts, self.inner, self.top, self.pairs)
-            k.linear(ctx, hidden, act, self.down_matrix, None, epilogue="add")
+            k.linear(ctx, hidden, act, self.down_matrix, None, epilogue="store" if assign else "add")
             return
         act = ctx.buffer("expert_act", (n * self.pairs, self.max_inner), ctx.act_dtype)
         k.experts(hidden, act, x, choice, in_weight, out_weight, self.gate_of, self.up_of, self.down_of, self.inner_of,
-                  self.max_inner, self.pairs, ld_down=self.total)
+                  self.max_inner, self.pairs, ld_down=self.total, assign=assign)
 
     def compute(self, ctx, x):
         out = ctx.buffer("mlp_out", (x.shape[0], self.width), torch.float32)
-        out.zero_()
-        self.forward(ctx, x, out)
+        self.forward(ctx, x, out, assign=True)
         return out
 
 

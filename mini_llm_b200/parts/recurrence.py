@@ -396,16 +396,16 @@ class ParallelMixers(Mixer):
     def compute(self, ctx, x, cache):
         """The weighted sum itself, in 32-bit, for arrangements that norm a mixer's output before the residual sum."""
         out = ctx.buffer("parallel_out", tuple(x.shape), torch.float32)      # (every mixer maps the width onto itself)
-        out.zero_()
         if len(self.branches) == 2:
             # two sides: both results go into the sum in one pass
             (name_a, part_a, scale_a), (name_b, part_b, scale_b) = self.branches
             mine = lambda name, part: cache.sub(name) if isinstance(part.cache_need(), dict) else cache.of(name)
             first, second = part_a.compute(ctx, x, mine(name_a, part_a)), part_b.compute(ctx, x, mine(name_b, part_b))
             if first.data_ptr() != second.data_ptr():
-                ctx.kernels.scaled_add(out, first, scale_a, second, scale_b)
+                ctx.kernels.scaled_add(out, first, scale_a, second, scale_b, assign=True)
                 return out
             raise RuntimeError(f"{self.prefix}: the two mixers hand over their results in one buffer")
+        out.zero_()
         self.forward(ctx, x, out, cache)
         return out
 
