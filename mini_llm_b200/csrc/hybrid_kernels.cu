@@ -476,6 +476,278 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
     }
 }
 
+// ---------------------------------------------------------------------------
+// The same attention as register tiles, for the common sizes (values of 64 or 128 entries, keys of up to 128,
+// no gate, no mask of blocks).  A block of 256 threads takes 64 (token, head) rows of one key/value head and walks
+// the keys 64 at a time.  Thread (ty, tx) of a 16 x 16 grid holds the scores of rows 4 ty .. 4 ty + 3 against keys
+// tx, tx + 16, tx + 32, tx + 48 (sixteen sums, fed by 16-byte reads of q and k rows along the head: eight FMAs a
+// read), then, after the block's softmax step, the sums of those rows' values for columns 4 tx .. 4 tx + 3 (and
+// 64 + 4 tx .. for values of 128): again sixteen (thirty-two) sums fed by 16-byte reads of the weights' rows and
+// of the values' rows.  The sixteen threads of a row lie in one half of a warp: a row's maximum and sum are four
+// shuffles, and its weights pass through shared memory between threads of one warp.  Scores, maxima, sums and
+// weights are 32-bit.  Tokens of several requests in a tile are taken request by request, as in the kernel above.
+// ---------------------------------------------------------------------------
+constexpr int BLOCK_ROWS = 64, BLOCK_KEYS = 64;
+constexpr int BLOCK_RT = 4;                                   // rows a thread (eight measured slower: 255 registers, one block fewer an SM)
+constexpr int BLOCK_THREADS = 16 * BLOCK_ROWS / BLOCK_RT;
+
+template <typename T, int VG>          // VG: 64-entry groups of a value (1 or 2)
+__global__ void __launch_bounds__(BLOCK_THREADS)
+capped_attention_block_kernel(T* __restrict__ out, long ld_out, const T* __restrict__ q, long ld_q,
+                              const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+                              const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
+                              const int* __restrict__ token_item, int n_tokens, int n_heads, int n_kv_heads, int dim,
+                              int page_size, float scale, float cap, int window, const float* __restrict__ sink,
+                              int tokens_per_block, int heads_per_block) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
+    constexpr int VDIM = 64 * VG;
+    extern __shared__ float shared[];
+    const int kd = dim + 4, vd = VDIM + 4, pd = BLOCK_KEYS + 4;
+    float* q_rows = shared;                                  // [64][kd]
+    float* keys = q_rows + BLOCK_ROWS * kd;                  // [64][kd]
+    float* values = keys + BLOCK_KEYS * kd;                  // [64][vd]
+    float* weights = values + BLOCK_KEYS * vd;               // [64][pd]
+    int* row_pos = reinterpret_cast<int*>(weights + BLOCK_ROWS * pd);     // [64]
+    int* row_item = row_pos + BLOCK_ROWS;                    // [64]
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int group = n_heads / n_kv_heads;
+    const int chunks = (group + heads_per_block - 1) / heads_per_block;
+    const int hk = blockIdx.y / chunks;
+    const int first_head = hk * group + (blockIdx.y % chunks) * heads_per_block;
+    const int n_heads_here = min(heads_per_block, hk * group + group - first_head);
+    // the step's last tokens first: within a request they see the most keys, and a long block that starts last would
+    // leave the other SMs idle at the end
+    const int first_token = (gridDim.x - 1 - blockIdx.x) * tokens_per_block;
+    const int n_tok = min(tokens_per_block, n_tokens - first_token);
+    const int n_rows = n_tok * n_heads_here;
+    const float inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
+    constexpr int VEC = 16 / (int)sizeof(T);
+
+    for (int r = tid; r < BLOCK_ROWS; r += blockDim.x) {
+        const bool live = r < n_rows;
+        const int token = live ? first_token + r / n_heads_here : 0;
+        row_pos[r] = live ? positions[token] : -1;
+        row_item[r] = live ? token_item[token] : -1;
+    }
+    for (int u = tid; u < BLOCK_ROWS * (dim / VEC); u += blockDim.x) {
+        const int r = u / (dim / VEC), d = (u % (dim / VEC)) * VEC;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < n_rows)
+            v = *reinterpret_cast<const uint4*>(q + (long)(first_token + r / n_heads_here) * ld_q + (long)(first_head + r % n_heads_here) * dim + d);
+        widen<T>(v, q_rows + r * kd + d);
+    }
+    __syncthreads();
+    constexpr int RT = BLOCK_RT;
+    int my_pos[RT], my_item[RT], my_first[RT];
+    float m[RT], l[RT], o[RT][4 * VG];
+#pragma unroll
+    for (int i = 0; i < RT; i++) {
+        my_pos[i] = row_pos[ty * RT + i], my_item[i] = row_item[ty * RT + i];
+        my_first[i] = first_visible(my_pos[i], window, 0);
+        m[i] = -INFINITY, l[i] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 4 * VG; c++) o[i][c] = 0.0f;
+    }
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
+    // A tile of 64 keys and values comes in 16-byte vectors, a fixed few of each per thread, asked for a tile ahead;
+    // which (key, column) a thread's vectors are is fixed for the kernel.
+    constexpr int MAXK = BLOCK_KEYS * 128 / VEC / BLOCK_THREADS, MAXV = BLOCK_KEYS * VDIM / VEC / BLOCK_THREADS;
+    uint4 key_vec[MAXK], value_vec[MAXV];
+    int key_row[MAXK], key_col[MAXK], value_row[MAXV], value_col[MAXV];
+#pragma unroll
+    for (int i = 0; i < MAXK; i++) {
+        const int u = tid + i * BLOCK_THREADS;
+        key_row[i] = u < BLOCK_KEYS * (dim / VEC) ? u / (dim / VEC) : -1;
+        key_col[i] = (u % (dim / VEC)) * VEC;
+        key_vec[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int i = 0; i < MAXV; i++) {
+        const int u = tid + i * BLOCK_THREADS;
+        value_row[i] = u / (VDIM / VEC);
+        value_col[i] = (u % (VDIM / VEC)) * VEC;
+        value_vec[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    auto fetch = [&](const int* bt, int base, int p_last, int p_lo) {
+#pragma unroll
+        for (int i = 0; i < MAXK; i++) {
+            const int kp = base + key_row[i];
+            key_vec[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (key_row[i] >= 0 && kp <= p_last && kp >= p_lo) {          // (pages before the first visible key may be gone)
+                const int block = page_shift >= 0 ? kp >> page_shift : kp / page_size;
+                const long slot = (long)bt[block] * page_size + (kp - block * page_size);
+                key_vec[i] = *reinterpret_cast<const uint4*>(k_pages + (slot * n_kv_heads + hk) * dim + key_col[i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < MAXV; i++) {
+            const int vp = base + value_row[i];
+            value_vec[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (vp <= p_last && vp >= p_lo) {
+                const int block = page_shift >= 0 ? vp >> page_shift : vp / page_size;
+                const long slot = (long)bt[block] * page_size + (vp - block * page_size);
+                value_vec[i] = *reinterpret_cast<const uint4*>(v_pages + (slot * n_kv_heads + hk) * VDIM + value_col[i]);
+            }
+        }
+    };
+
+    int run_first = 0;
+    while (run_first < n_tok) {
+        const int item = token_item[first_token + run_first];
+        int run_last = run_first;
+        while (run_last + 1 < n_tok && token_item[first_token + run_last + 1] == item) run_last++;
+        const int p_first = positions[first_token + run_first], p_last = positions[first_token + run_last];
+        const int lo = first_visible(p_first, window, 0);
+        const int* bt = block_table + (long)item * max_blocks;
+        const int first_base = (lo / BLOCK_KEYS) * BLOCK_KEYS;
+        fetch(bt, first_base, p_last, lo);
+        for (int base = first_base; base <= p_last; base += BLOCK_KEYS) {
+            __syncthreads();                                  // the tile before has been read
+#pragma unroll
+            for (int i = 0; i < MAXK; i++)
+                if (key_row[i] >= 0) widen<T>(key_vec[i], keys + key_row[i] * kd + key_col[i]);
+#pragma unroll
+            for (int i = 0; i < MAXV; i++) widen<T>(value_vec[i], values + value_row[i] * vd + value_col[i]);
+            __syncthreads();
+            // the next tile's rows are asked for now and arrive while this one is worked on
+            if (base + BLOCK_KEYS <= p_last) fetch(bt, base + BLOCK_KEYS, p_last, lo);
+            // does any row of this warp see a key of this tile?
+            bool any = false;
+#pragma unroll
+            for (int i = 0; i < RT; i++)
+                any = any || (my_item[i] == item && base <= my_pos[i] && base + BLOCK_KEYS > my_first[i]);
+            if (!__any_sync(0xffffffffu, any)) continue;      // (uniform in the warp; the barriers are at the loop's head)
+            float acc[RT][4];
+#pragma unroll
+            for (int i = 0; i < RT; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+#pragma unroll 2
+            for (int d = 0; d < dim; d += 4) {
+                float4 a[RT], b[4];
+#pragma unroll
+                for (int i = 0; i < RT; i++) a[i] = *reinterpret_cast<const float4*>(q_rows + (ty * RT + i) * kd + d);
+#pragma unroll
+                for (int j = 0; j < 4; j++) b[j] = *reinterpret_cast<const float4*>(keys + (tx + 16 * j) * kd + d);
+#pragma unroll
+                for (int i = 0; i < RT; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
+                        acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
+                        acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
+                        acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+                    }
+            }
+#pragma unroll
+            for (int i = 0; i < RT; i++) {
+                const bool row_here = my_item[i] == item;
+                float score[4], top = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int pos = base + tx + 16 * j;
+                    const bool seen = row_here && pos <= my_pos[i] && pos >= my_first[i];
+                    score[j] = seen ? capped(acc[i][j] * scale, cap, inv_cap) : -INFINITY;
+                    top = fmaxf(top, score[j]);
+                }
+#pragma unroll
+                for (int step = 8; step > 0; step >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, step));
+                float rescale = 1.0f, e[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sum = 0.0f;
+                if (top != -INFINITY) {
+                    const float m_new = fmaxf(m[i], top);
+                    rescale = expf(m[i] - m_new);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        e[j] = score[j] == -INFINITY ? 0.0f : expf(score[j] - m_new);
+                        sum += e[j];
+                    }
+                    m[i] = m_new;
+                }
+#pragma unroll
+                for (int step = 8; step > 0; step >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, step);
+                l[i] = l[i] * rescale + sum;
+#pragma unroll
+                for (int c = 0; c < 4 * VG; c++) o[i][c] *= rescale;
+#pragma unroll
+                for (int j = 0; j < 4; j++) weights[(ty * RT + i) * pd + tx + 16 * j] = e[j];
+            }
+            __syncwarp();                                     // a row's sixteen threads lie in this warp
+#pragma unroll 2
+            for (int j = 0; j < BLOCK_KEYS; j += 4) {
+                float4 w[RT];
+#pragma unroll
+                for (int i = 0; i < RT; i++) w[i] = *reinterpret_cast<const float4*>(weights + (ty * RT + i) * pd + j);
+#pragma unroll
+                for (int jj = 0; jj < 4; jj++) {
+#pragma unroll
+                    for (int g = 0; g < VG; g++) {
+                        const float4 v = *reinterpret_cast<const float4*>(values + (j + jj) * vd + 64 * g + tx * 4);
+#pragma unroll
+                        for (int i = 0; i < RT; i++) {
+                            const float p = jj == 0 ? w[i].x : (jj == 1 ? w[i].y : (jj == 2 ? w[i].z : w[i].w));
+                            o[i][4 * g] = fmaf(p, v.x, o[i][4 * g]);
+                            o[i][4 * g + 1] = fmaf(p, v.y, o[i][4 * g + 1]);
+                            o[i][4 * g + 2] = fmaf(p, v.z, o[i][4 * g + 2]);
+                            o[i][4 * g + 3] = fmaf(p, v.w, o[i][4 * g + 3]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();                                     // the weights are read before the next tile's are written
+        }
+        run_first = run_last + 1;
+    }
+#pragma unroll
+    for (int i = 0; i < RT; i++) {
+        const int r = ty * RT + i;
+        if (r >= n_rows) continue;
+        const int token = first_token + r / n_heads_here, head = first_head + r % n_heads_here;
+        float sum = l[i], shrink = 1.0f;
+        if (sink != nullptr) {
+            const float top = fmaxf(m[i], sink[head]);
+            shrink = expf(m[i] - top);
+            sum = sum * shrink + expf(sink[head] - top);
+        }
+        const float inv = shrink / sum;
+#pragma unroll
+        for (int g = 0; g < VG; g++)
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+                out[(long)token * ld_out + (long)head * VDIM + 64 * g + tx * 4 + c] = from_f32<T>(o[i][4 * g + c] * inv);
+    }
+}
+
+static size_t capped_block_shared(int dim, int vdim) {
+    return sizeof(float) * ((size_t)2 * BLOCK_ROWS * (dim + 4) + (size_t)BLOCK_KEYS * (vdim + 4) + (size_t)BLOCK_ROWS * (BLOCK_KEYS + 4)) +
+           sizeof(int) * 2 * BLOCK_ROWS;
+}
+
+// (keys in whole 16-byte vectors, values of 64 or 128 entries)
+static bool capped_block_takes(int dim, int vdim, int vec) {
+    return dim > 0 && dim <= 128 && dim % vec == 0 && dim % 4 == 0 && (vdim == 64 || vdim == 128);
+}
+
+template <typename T, int VG>
+static int launch_capped_block(void* out, long ld_out, const void* q, long ld_q, const void* k_pages, const void* v_pages,
+                               const int* block_table, int max_blocks, const int* positions, const int* token_item, int n_tokens,
+                               int n_heads, int n_kv_heads, int dim, int page_size, float scale, float cap, int window,
+                               const float* sink, cudaStream_t s) {
+    const int group = n_heads / n_kv_heads;
+    const int heads_per_block = group < BLOCK_ROWS ? group : BLOCK_ROWS;
+    const int tokens_per_block = BLOCK_ROWS / heads_per_block;
+    const int chunks = (group + heads_per_block - 1) / heads_per_block;
+    const size_t shared = capped_block_shared(dim, 64 * VG);
+    cudaError_t e = cudaFuncSetAttribute(capped_attention_block_kernel<T, VG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    if (e != cudaSuccess) return fail("capped_attention: the register tiles' shared memory was refused");
+    cudaFuncSetAttribute(capped_attention_block_kernel<T, VG>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    dim3 grid((n_tokens + tokens_per_block - 1) / tokens_per_block, n_kv_heads * chunks);
+    launch_kernel(g_dependent_launch != 0, capped_attention_block_kernel<T, VG>, grid, dim3(BLOCK_THREADS), shared, s, (T*)out, ld_out, (const T*)q,
+                  ld_q, (const T*)k_pages, (const T*)v_pages, block_table, max_blocks, positions, token_item, n_tokens, n_heads,
+                  n_kv_heads, dim, page_size, scale, cap, window, sink, tokens_per_block, heads_per_block);
+    return check_launch("capped_attention_block_kernel");
+}
+
 static size_t capped_tiled_shared(int dim, int vdim, int rows_per_warp) {
     return sizeof(float) * ((size_t)TILE_WARPS * rows_per_warp * dim + (size_t)TILE_KEYS * (dim + 4) + (size_t)TILE_KEYS * vdim +
                             (size_t)TILE_WARPS * TILE_KEYS * rows_per_warp);
@@ -521,6 +793,15 @@ static int launch_capped_attention(bool tiled, void* out, long ld_out, const voi
                       ld_out, (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table, max_blocks, positions,
                       token_item, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, chunk, gate, ld_gate, sink);
         return check_launch("capped_attention_plain_kernel");
+    }
+    // the common sizes go to the register tiles
+    if (gate == nullptr && chunk == 0 && n_tokens * (long)n_heads >= 2048 && capped_block_takes(dim, vdim, 16 / (int)sizeof(T)) &&
+        (ld_q * sizeof(T)) % 16 == 0) {
+        if (vdim == 64)
+            return launch_capped_block<T, 1>(out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions, token_item,
+                                             n_tokens, n_heads, n_kv_heads, dim, page_size, scale, cap, window, sink, s);
+        return launch_capped_block<T, 2>(out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions, token_item,
+                                         n_tokens, n_heads, n_kv_heads, dim, page_size, scale, cap, window, sink, s);
     }
     // rows a warp: four where the step has rows enough for the blocks to fill the GPU all the same
     // (and their shared memory fits), else two

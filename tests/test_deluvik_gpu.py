@@ -328,6 +328,44 @@ def test_attention_kernels_with_a_sink(heads, kv_heads, dim, vdim, window, cap):
     assert np.abs(expected - plain.attend(q, k, v, 0.4, cap or None, window or None, None).reshape(n, -1)).max() > 0.05
 
 
+@pytest.mark.parametrize("heads, kv_heads, dim, vdim, window, cap, dtype", [
+    (4, 2, 64, 64, 0, 0.0, torch.float32), (6, 1, 32, 128, 50, 3.0, torch.float32), (4, 4, 128, 64, 200, 0.0, torch.float32),
+    (6, 2, 64, 64, 0, 20.0, torch.bfloat16)])
+def test_attention_in_register_tiles(heads, kv_heads, dim, vdim, window, cap, dtype):
+    """Steps with thousands of (token, head) rows take the kernel with register tiles: two requests whose border
+    falls inside a tile (the second one's portion starts at position 40 of its sequence), against the formula."""
+    from mini_llm_b200.kernels import ops
+    rng = np.random.default_rng(dim + vdim)
+    page, n0, n1, start1 = 16, 333, 360, 40
+    cases = [_attention_case(rng, n0, heads, kv_heads, dim, vdim, page, dtype), _attention_case(rng, n1, heads, kv_heads, dim, vdim, page, dtype, start=start1)]
+    # one pool for both requests: the second one's pages lie behind the first one's
+    shift = cases[0][3].shape[0]
+    k_pages, v_pages = torch.cat([cases[0][3], cases[1][3]]), torch.cat([cases[0][4], cases[1][4]])
+    width = max(cases[0][5].shape[1], cases[1][5].shape[1])
+    table = torch.zeros((2, width), dtype=torch.int32, device="cuda")
+    table[0, :cases[0][5].shape[1]] = cases[0][5][0]
+    table[1, :cases[1][5].shape[1]] = cases[1][5][0] + shift
+    positions = torch.cat([cases[0][6], cases[1][6]])
+    items = torch.cat([torch.zeros(n0), torch.ones(n1 - start1)]).to(torch.int32).cuda()
+    q = np.concatenate([cases[0][0], cases[1][0][start1:]])
+    n = q.shape[0]
+    assert n * heads >= 2048
+    sink = np.linspace(-3.0, 4.0, heads)
+    expected = np.concatenate([plain.attend(cases[0][0], cases[0][1], cases[0][2], 0.3, cap or None, window or None, sink),
+                               plain.attend(cases[1][0][start1:], cases[1][1], cases[1][2], 0.3, cap or None, window or None, sink,
+                                            first_position=start1)]).reshape(n, heads * vdim)
+    out = torch.empty((n, heads * vdim), dtype=dtype, device="cuda")
+    ops.capped_attention(out, dev(q.reshape(n, -1), dtype), k_pages, v_pages, table, positions, items, heads, kv_heads, dim, vdim, page, 0.3,
+                         cap, window, tiled=True, sink=dev(sink))
+    np.testing.assert_allclose(out.float().cpu().numpy(), expected, atol=2e-5 if dtype == torch.float32 else 0.02)
+    # the same rows through the tiles of few rows (a gate of +40 everywhere opens every head fully and keeps them there)
+    gate = torch.full((n, heads), 40.0, device="cuda")
+    again = torch.empty_like(out)
+    ops.capped_attention(again, dev(q.reshape(n, -1), dtype), k_pages, v_pages, table, positions, items, heads, kv_heads, dim, vdim, page,
+                         0.3, cap, window, tiled=True, sink=dev(sink), gate=gate)
+    np.testing.assert_allclose(again.float().cpu().numpy(), expected, atol=2e-5 if dtype == torch.float32 else 0.02)
+
+
 def test_split_attention_with_a_sink():
     """Single tokens over split keys (bfloat16): the sink joins the merge of the chunks."""
     from mini_llm_b200.kernels import ops
