@@ -7,7 +7,7 @@ whose entries give ``type``, ``mixer`` (its sizes and constants) and ``mlp``:
   with ``factor``, ``low``, ``high``, ``original``), optional ``softcap``; the values are the keys as projected, so
   ``vdim`` equals ``dim``;
 * ``type`` "attention_2": the same keys, plus ``conv`` (taps of the short convolution on q, k and v) and optionally
-  ``kv_from`` (an earlier "attention_2" layer whose keys and values this layer reads instead of its own);
+  ``kv_from`` (an earlier attention layer whose keys and values this layer reads instead of its own);
 * ``type`` "parallel": ``left`` (an attention with ``mask.size``, the sliding window), ``right`` (``width``, ``blocks``,
   ``conv``: the gated linear recurrence), ``left_scale`` and ``right_scale``;
 * ``mlp``: null, ``{"kind": "dense", "ff"}`` or ``{"kind": "moe", "router": {"experts", "top"}, "expert": {"ff"},
@@ -126,8 +126,8 @@ def read_layer(raw, index: int) -> dict:
 
 
 def check_shared_rows(layers) -> None:
-    """A layer with ``kv_from`` names an earlier layer of its own type that has keys and values of its own, with
-    the same key/value heads, sizes and rotation."""
+    """A layer with ``kv_from`` names an earlier attention layer that has keys and values of its own, with the same
+    key/value heads and sizes (what the shared pages must agree on)."""
     for index, layer in enumerate(layers):
         source = layer["mixer"].get("kv_from") if layer["type"] != "parallel" else None
         if source is None:
@@ -136,10 +136,9 @@ def check_shared_rows(layers) -> None:
         if not 0 <= source < index:
             raise ConfigError(f"config key '{where}': {source} is not an earlier layer")
         other = layers[source]
-        if other["type"] != layer["type"] or other["mixer"].get("kv_from") is not None:
-            raise ConfigError(f"config key '{where}': layer {source} is not a layer of type '{layer['type']}' with keys and "
-                              f"values of its own")
-        for key in ("kv_heads", "dim", "vdim", "rot"):
+        if other["type"] == "parallel" or other["mixer"].get("kv_from") is not None:
+            raise ConfigError(f"config key '{where}': layer {source} is not an attention layer with keys and values of its own")
+        for key in ("kv_heads", "dim", "vdim"):
             if other["mixer"][key] != layer["mixer"][key]:
                 raise ConfigError(f"config key '{where}': layer {source} has another '{key}' ({other['mixer'][key]!r}) than this "
                                   f"layer ({layer['mixer'][key]!r})")
